@@ -1,0 +1,554 @@
+// Token-major data movers of the MoE hot path. Each work item owns a tile of
+// one token row and walks the routed rows that belong to it, so every byte of
+// payload crosses HBM once and every output element is written once:
+//   combine forward   out[t]       = sum_j src_j * w_j            (plan order)
+//   combine backward  grad_rows[g] = grad_out[t] * w_g ; grad_w[g] = <grad_out[t], src_g>
+//   dispatch permute  permuted[slot_of[t,k]] = x[t]
+//   permute backward  grad_x[t]    = sum_k grad_permuted[slot_of[t,k]]
+// They replace, in polkadot21/fastmoe: the Triton scatter-add kernel
+// (src/fastmoe/kernels/ops.py:57-194), GroupedWeightedScatterAdd.backward
+// (ops.py:334-359), the row gather x_flat[reverse_map]
+// (src/fastmoe/models/tiny_model.py:133) and its autograd backward.
+#include <string_view>
+
+#include "plan.cuh"
+
+namespace fmoe {
+
+// ---- tuning knobs (fmoe_tune) -------------------------------------------------
+static int g_gather_v = 0;         // vectors per thread, 0 = choose from D
+static int g_gather_threads = 0;   // threads per CTA, 0 = choose from D
+static int g_gather_ctas_per_sm = 0;  // persistent grid = 148 * this; 0 = one CTA per item
+static int g_bwd_ctas_per_sm = 4;
+
+struct TileCfg {
+  int threads;
+  int v;
+  int tiles;
+};
+
+// Picks threads-per-CTA (a multiple of 32) and vectors-per-thread so that a row
+// of `dvec` 16-byte vectors splits into whole tiles with the fewest idle lanes.
+static TileCfg pick_tile(int64_t dvec, int pref_v, int force_threads, int max_v = 4) {
+  TileCfg best{32, 1, static_cast<int>(dvec)};
+  double best_score = -1.0;
+  for (int threads = 32; threads <= 256; threads += 32) {
+    if (force_threads > 0 && threads != force_threads) continue;
+    for (int v = 1; v <= max_v; v *= 2) {
+      const int64_t span = static_cast<int64_t>(threads) * v;
+      const int64_t tiles = (dvec + span - 1) / span;
+      const double eff = static_cast<double>(dvec) / static_cast<double>(tiles * span);
+      // prefer full lanes, then the preferred vector count, then wide CTAs
+      const double score = eff * 1000.0 + (v == pref_v ? 1.0 : 0.0) + threads / 1024.0;
+      if (score > best_score) {
+        best_score = score;
+        best = TileCfg{threads, v, static_cast<int>(tiles)};
+      }
+    }
+  }
+  return best;
+}
+
+// ---- row sources ----------------------------------------------------------------
+// A source tells, for output row t, which slots feed it, and for a slot, where
+// its row lives and what it is scaled by.
+struct PlanSource {
+  const int32_t* seg_off;
+  const int64_t* src_sorted;
+  const float* w_sorted;
+  __device__ __forceinline__ void segment(int64_t t, int& beg, int& end) const {
+    beg = seg_off[t];
+    end = seg_off[t + 1];
+  }
+  __device__ __forceinline__ void row(int j, const char*& p, float& w) const {
+    p = reinterpret_cast<const char*>(src_sorted[j]);
+    w = w_sorted[j];
+  }
+};
+
+struct SlotSource {  // K rows of one matrix per token, unit weights
+  const int32_t* slot_of;
+  const char* base;
+  int64_t row_bytes;
+  int64_t rows;  // rows of the matrix (bounds check)
+  int K;
+  __device__ __forceinline__ void segment(int64_t t, int& beg, int& end) const {
+    beg = static_cast<int>(t * K);
+    end = beg + K;
+  }
+  __device__ __forceinline__ void row(int j, const char*& p, float& w) const {
+    const int32_t s = slot_of[j];
+    p = (s >= 0 && s < rows) ? base + s * row_bytes : nullptr;
+    w = 1.f;
+  }
+};
+
+template <int DT>
+__device__ __forceinline__ uint4 load_row_vec(const char* p, int64_t col) {
+  using El = Elem<DT>;
+  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0)
+    return ld_stream16(reinterpret_cast<const uint4*>(p) + col);
+  uint4 x;  // odd base address: element loads
+  const typename El::type* s = reinterpret_cast<const typename El::type*>(p) + col * El::kVec;
+  typename El::type* d = reinterpret_cast<typename El::type*>(&x);
+#pragma unroll
+  for (int i = 0; i < El::kVec; ++i) d[i] = s[i];
+  return x;
+}
+
+// ---- gather-sum: combine forward and permute backward --------------------------------
+template <int DT, int V, bool WEIGHTED, class Source>
+__global__ void __launch_bounds__(256)
+    gather_sum_kernel(const Source src, void* __restrict__ out, int64_t out_row_stride, int64_t T,
+                      int64_t dvec, int tiles, int accumulate) {
+  using El = Elem<DT>;
+  using Ty = typename El::type;
+  constexpr int U = 4;  // rows in flight
+  const int64_t items = T * tiles;
+  for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+    const int64_t t = item / tiles;
+    const int tile = static_cast<int>(item - t * tiles);
+    int64_t col[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) col[v] = (static_cast<int64_t>(tile) * V + v) * blockDim.x + threadIdx.x;
+
+    int beg, end;
+    src.segment(t, beg, end);
+
+    float acc[V][El::kVec];
+    uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<Ty*>(out) + t * out_row_stride);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      if (accumulate && col[v] < dvec) {
+        unpack16<DT>(orow[col[v]], acc[v]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < El::kVec; ++i) acc[v][i] = 0.f;
+      }
+    }
+
+    int j = beg;
+    for (; j + U <= end; j += U) {
+      const char* p[U];
+      float w[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) src.row(j + u, p[u], w[u]);
+      uint4 x[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+          x[u][v] = (p[u] != nullptr && col[v] < dvec) ? load_row_vec<DT>(p[u], col[v])
+                                                       : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          float f[El::kVec];
+          unpack16<DT>(x[u][v], f);
+#pragma unroll
+          for (int i = 0; i < El::kVec; ++i)
+            acc[v][i] = WEIGHTED ? __fadd_rn(acc[v][i], __fmul_rn(f[i], w[u]))
+                                 : __fadd_rn(acc[v][i], f[i]);
+        }
+    }
+    for (; j < end; ++j) {
+      const char* p;
+      float w;
+      src.row(j, p, w);
+      uint4 x[V];
+#pragma unroll
+      for (int v = 0; v < V; ++v)
+        x[v] = (p != nullptr && col[v] < dvec) ? load_row_vec<DT>(p, col[v]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        float f[El::kVec];
+        unpack16<DT>(x[v], f);
+#pragma unroll
+        for (int i = 0; i < El::kVec; ++i)
+          acc[v][i] = WEIGHTED ? __fadd_rn(acc[v][i], __fmul_rn(f[i], w)) : __fadd_rn(acc[v][i], f[i]);
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+      if (col[v] < dvec) st_stream16(orow + col[v], pack16<DT>(acc[v]));
+  }
+}
+
+// Element-wise variant for widths or layouts that rule out 16-byte accesses.
+template <int DT, bool WEIGHTED, class Source>
+__global__ void __launch_bounds__(256)
+    gather_sum_scalar_kernel(const Source src, void* __restrict__ out, int64_t out_row_stride,
+                             int64_t T, int64_t D, int accumulate) {
+  using Ty = typename Elem<DT>::type;
+  const int64_t total = T * D;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / D, c = i - t * D;
+    Ty* o = reinterpret_cast<Ty*>(out) + t * out_row_stride + c;
+    float acc = accumulate ? to_float<DT>(*o) : 0.f;
+    int beg, end;
+    src.segment(t, beg, end);
+    for (int j = beg; j < end; ++j) {
+      const char* p;
+      float w;
+      src.row(j, p, w);
+      if (p == nullptr) continue;
+      const float f = to_float<DT>(reinterpret_cast<const Ty*>(p)[c]);
+      acc = WEIGHTED ? __fadd_rn(acc, __fmul_rn(f, w)) : __fadd_rn(acc, f);
+    }
+    *o = from_float<DT>(acc);
+  }
+}
+
+template <int DT, bool WEIGHTED, class Source>
+static int launch_gather_sum(const Source& src, void* out, int64_t out_row_stride, int64_t T,
+                             int64_t D, int accumulate, cudaStream_t s) {
+  using El = Elem<DT>;
+  if (T == 0 || D == 0) return FMOE_OK;
+  const bool vec_ok =
+      (D % El::kVec == 0) && aligned_to(out, 16) && ((out_row_stride * El::kBytes) % 16 == 0);
+  if (!vec_ok) {
+    const int64_t blocks = (T * D + 255) / 256;
+    const int grid = static_cast<int>(blocks < kNumSMs * 16 ? blocks : kNumSMs * 16);
+    gather_sum_scalar_kernel<DT, WEIGHTED, Source><<<grid, 256, 0, s>>>(src, out, out_row_stride, T, D, accumulate);
+    return check_launch("gather_sum_scalar_kernel");
+  }
+  const int64_t dvec = D / El::kVec;
+  const TileCfg cfg = pick_tile(dvec, g_gather_v > 0 ? g_gather_v : 2, g_gather_threads);
+  const int64_t items = T * cfg.tiles;
+  int64_t grid = items;
+  if (g_gather_ctas_per_sm > 0 && items > static_cast<int64_t>(kNumSMs) * g_gather_ctas_per_sm)
+    grid = static_cast<int64_t>(kNumSMs) * g_gather_ctas_per_sm;
+  if (grid > 0x7fffffffll) grid = 0x7fffffffll;
+  const int g = static_cast<int>(grid);
+  switch (cfg.v) {
+    case 1:
+      gather_sum_kernel<DT, 1, WEIGHTED, Source><<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);
+      break;
+    case 2:
+      gather_sum_kernel<DT, 2, WEIGHTED, Source><<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);
+      break;
+    default:
+      gather_sum_kernel<DT, 4, WEIGHTED, Source><<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);
+      break;
+  }
+  return check_launch("gather_sum_kernel");
+}
+
+// ---- combine backward ---------------------------------------------------------------
+// One CTA per output row: grad_out[t] is read once per chunk of 8 routed rows,
+// each routed row gets its scaled copy, and the gate gradient is the row dot
+// with the forward source row, reduced across the CTA in a fixed order.
+constexpr int kBwdRows = 8;
+
+template <int DT, int V, bool WITH_GW>
+__global__ void __launch_bounds__(256)
+    combine_bwd_kernel(const int32_t* __restrict__ seg_off, const int32_t* __restrict__ row_of_slot,
+                       const int64_t* __restrict__ src_sorted, const float* __restrict__ w_sorted,
+                       const void* __restrict__ grad_out, int64_t go_row_stride,
+                       void* __restrict__ grad_rows, float* __restrict__ grad_w, int64_t T,
+                       int64_t D, int64_t dvec, int tiles) {
+  using El = Elem<DT>;
+  using Ty = typename El::type;
+  __shared__ float red[8][kBwdRows];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+
+  for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
+    const int beg = seg_off[t], end = seg_off[t + 1];
+    const uint4* gorow = reinterpret_cast<const uint4*>(reinterpret_cast<const Ty*>(grad_out) + t * go_row_stride);
+    for (int jc = beg; jc < end; jc += kBwdRows) {
+      const int nj = min(kBwdRows, end - jc);
+      int64_t g[kBwdRows];
+      float w[kBwdRows];
+      const char* p[kBwdRows];
+      float dot[kBwdRows];
+#pragma unroll
+      for (int u = 0; u < kBwdRows; ++u) {
+        dot[u] = 0.f;
+        g[u] = -1;
+        w[u] = 0.f;
+        p[u] = nullptr;
+        if (u < nj) {
+          g[u] = row_of_slot[jc + u];
+          w[u] = w_sorted[jc + u];
+          p[u] = reinterpret_cast<const char*>(src_sorted[jc + u]);
+        }
+      }
+      for (int tile = 0; tile < tiles; ++tile) {
+        int64_t col[V];
+        float go[V][El::kVec];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          col[v] = (static_cast<int64_t>(tile) * V + v) * blockDim.x + threadIdx.x;
+          if (col[v] < dvec) {
+            unpack16<DT>(ld_keep16(gorow + col[v]), go[v]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < El::kVec; ++i) go[v][i] = 0.f;
+          }
+        }
+        uint4 x[kBwdRows][V];
+        if (WITH_GW) {
+#pragma unroll
+          for (int u = 0; u < kBwdRows; ++u)
+#pragma unroll
+            for (int v = 0; v < V; ++v)
+              x[u][v] = (p[u] != nullptr && col[v] < dvec) ? load_row_vec<DT>(p[u], col[v])
+                                                           : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kBwdRows; ++u) {
+          if (g[u] < 0) continue;
+          uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<Ty*>(grad_rows) + g[u] * D);
+#pragma unroll
+          for (int v = 0; v < V; ++v) {
+            if (col[v] >= dvec) continue;
+            float f[El::kVec];
+#pragma unroll
+            for (int i = 0; i < El::kVec; ++i) f[i] = __fmul_rn(go[v][i], w[u]);
+            st_stream16(drow + col[v], pack16<DT>(f));
+            if (WITH_GW) {
+              float xf[El::kVec];
+              unpack16<DT>(x[u][v], xf);
+#pragma unroll
+              for (int i = 0; i < El::kVec; ++i) dot[u] = fmaf(go[v][i], xf[i], dot[u]);
+            }
+          }
+        }
+      }
+      if (WITH_GW) {
+#pragma unroll
+        for (int u = 0; u < kBwdRows; ++u) {
+          float d = dot[u];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          if (lane == 0) red[warp][u] = d;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < kBwdRows; ++u) {
+          if (threadIdx.x == u && u < nj) {  // g[] is uniform across the CTA
+            float d = 0.f;
+            for (int wv = 0; wv < nwarps; ++wv) d += red[wv][u];
+            grad_w[g[u]] = d;
+          }
+        }
+        __syncthreads();
+      }
+    }
+  }
+}
+
+// ---- dispatch permute forward ----------------------------------------------------
+template <int DT, int V>
+__global__ void __launch_bounds__(256)
+    permute_fwd_kernel(const void* __restrict__ x, int64_t x_row_stride,
+                       const int32_t* __restrict__ slot_of, void* __restrict__ permuted, int64_t T,
+                       int K, int64_t D, int64_t dvec, int tiles) {
+  using El = Elem<DT>;
+  using Ty = typename El::type;
+  const int64_t items = T * tiles;
+  const int64_t rows = T * K;
+  for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+    const int64_t t = item / tiles;
+    const int tile = static_cast<int>(item - t * tiles);
+    const uint4* xrow = reinterpret_cast<const uint4*>(reinterpret_cast<const Ty*>(x) + t * x_row_stride);
+    uint4 val[V];
+    int64_t col[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      col[v] = (static_cast<int64_t>(tile) * V + v) * blockDim.x + threadIdx.x;
+      if (col[v] < dvec) val[v] = ld_stream16(xrow + col[v]);
+    }
+    for (int k = 0; k < K; ++k) {
+      const int32_t s = slot_of[t * K + k];
+      if (s < 0 || s >= rows) continue;
+      uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<Ty*>(permuted) + static_cast<int64_t>(s) * D);
+#pragma unroll
+      for (int v = 0; v < V; ++v)
+        if (col[v] < dvec) st_stream16(drow + col[v], val[v]);
+    }
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+    permute_fwd_scalar_kernel(const void* __restrict__ x, int64_t x_row_stride,
+                              const int32_t* __restrict__ slot_of, void* __restrict__ permuted,
+                              int64_t T, int K, int64_t D) {
+  using Ty = typename Elem<DT>::type;
+  const int64_t rows = T * K;
+  const int64_t total = rows * D;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t tk = i / D, c = i - tk * D;
+    const int32_t s = slot_of[tk];
+    if (s < 0 || s >= rows) continue;
+    reinterpret_cast<Ty*>(permuted)[static_cast<int64_t>(s) * D + c] =
+        reinterpret_cast<const Ty*>(x)[(tk / K) * x_row_stride + c];
+  }
+}
+
+static int64_t clamp_grid(int64_t items, int ctas_per_sm) {
+  int64_t grid = items;
+  if (ctas_per_sm > 0 && items > static_cast<int64_t>(kNumSMs) * ctas_per_sm)
+    grid = static_cast<int64_t>(kNumSMs) * ctas_per_sm;
+  if (grid > 0x7fffffffll) grid = 0x7fffffffll;
+  return grid;
+}
+
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" int fmoe_tune(const char* key, int value) {
+  if (key == nullptr) return FMOE_ERR_ARG;
+  const std::string_view k(key);
+  if (k == "gather_v") {
+    FMOE_REQUIRE(value == 0 || value == 1 || value == 2 || value == 4, FMOE_ERR_ARG,
+                 "fmoe_tune: gather_v must be 0, 1, 2 or 4");
+    g_gather_v = value;
+  } else if (k == "gather_threads") {
+    FMOE_REQUIRE(value >= 0 && value <= 256 && value % 32 == 0, FMOE_ERR_ARG,
+                 "fmoe_tune: gather_threads must be a multiple of 32 in [0, 256]");
+    g_gather_threads = value;
+  } else if (k == "gather_ctas_per_sm") {
+    FMOE_REQUIRE(value >= 0 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: gather_ctas_per_sm in [0, 64]");
+    g_gather_ctas_per_sm = value;
+  } else if (k == "bwd_ctas_per_sm") {
+    FMOE_REQUIRE(value >= 1 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: bwd_ctas_per_sm in [1, 64]");
+    g_bwd_ctas_per_sm = value;
+  } else {
+    return fail(FMOE_ERR_ARG, "fmoe_tune: unknown key '%s'", key);
+  }
+  return FMOE_OK;
+}
+
+extern "C" int fmoe_combine_gather(const void* plan, void* out, int64_t out_row_stride, int64_t N,
+                                   int64_t T, int64_t D, int dtype, int accumulate, void* stream) {
+  FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_combine_gather: bad dtype %d", dtype);
+  FMOE_REQUIRE(N >= 0 && T >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_combine_gather: negative size");
+  FMOE_REQUIRE(N < (1ll << 31) && T < (1ll << 31) - 1, FMOE_ERR_UNSUPPORTED,
+               "fmoe_combine_gather: N and T must fit in int32");
+  if (T == 0 || D == 0) return FMOE_OK;
+  FMOE_REQUIRE(plan != nullptr && aligned_to(plan, 256), FMOE_ERR_WORKSPACE,
+               "fmoe_combine_gather: plan is null or not 256-byte aligned");
+  FMOE_REQUIRE(out != nullptr, FMOE_ERR_ARG, "fmoe_combine_gather: out is null");
+  FMOE_REQUIRE(out_row_stride >= D, FMOE_ERR_ARG, "fmoe_combine_gather: out_row_stride %lld < D %lld",
+               (long long)out_row_stride, (long long)D);
+  const PlanView pv = plan_view(const_cast<void*>(plan), N, T);
+  const PlanSource src{pv.seg_off, pv.src_sorted, pv.w_sorted};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = 0;
+  FMOE_DISPATCH_DTYPE(dtype, DT,
+                      rc = (launch_gather_sum<DT, true, PlanSource>(src, out, out_row_stride, T, D,
+                                                                    accumulate != 0, s)));
+  return rc;
+}
+
+extern "C" int fmoe_combine_bwd(const void* plan, const void* grad_out, int64_t grad_out_row_stride,
+                                void* grad_rows, float* grad_w, int64_t N, int64_t T, int64_t D,
+                                int dtype, void* stream) {
+  FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_combine_bwd: bad dtype %d", dtype);
+  FMOE_REQUIRE(N >= 0 && T >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_combine_bwd: negative size");
+  FMOE_REQUIRE(N < (1ll << 31) && T < (1ll << 31) - 1, FMOE_ERR_UNSUPPORTED,
+               "fmoe_combine_bwd: N and T must fit in int32");
+  if (N == 0 || T == 0) return FMOE_OK;
+  FMOE_REQUIRE(plan != nullptr && aligned_to(plan, 256), FMOE_ERR_WORKSPACE,
+               "fmoe_combine_bwd: plan is null or not 256-byte aligned");
+  FMOE_REQUIRE(grad_out != nullptr && grad_rows != nullptr, FMOE_ERR_ARG,
+               "fmoe_combine_bwd: null pointer argument");
+  FMOE_REQUIRE(grad_out_row_stride >= D, FMOE_ERR_ARG, "fmoe_combine_bwd: grad_out_row_stride < D");
+  const int eb = dtype_size(dtype);
+  const int kvec = 16 / eb;
+  FMOE_REQUIRE(D % kvec == 0 && aligned_to(grad_out, 16) && aligned_to(grad_rows, 16) &&
+                   (grad_out_row_stride * eb) % 16 == 0,
+               FMOE_ERR_UNSUPPORTED,
+               "fmoe_combine_bwd: D must be a multiple of %d and buffers 16-byte aligned", kvec);
+  const PlanView pv = plan_view(const_cast<void*>(plan), N, T);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 0) {
+    if (grad_w != nullptr) FMOE_CUDA(cudaMemsetAsync(grad_w, 0, sizeof(float) * N, s));
+    return FMOE_OK;
+  }
+  // rows that were skipped when the plan was built (bad index) get no slot:
+  // their gate gradient must still be defined
+  if (grad_w != nullptr) FMOE_CUDA(cudaMemsetAsync(grad_w, 0, sizeof(float) * N, s));
+  const int64_t dvec = D / kvec;
+  const TileCfg cfg = pick_tile(dvec, 1, 0, /*max_v=*/1);  // 8 rows x 1 vector in flight per thread
+  const int grid = static_cast<int>(clamp_grid(T, g_bwd_ctas_per_sm));
+  int rc = 0;
+#define FMOE_BWD_LAUNCH(DT, V, GW)                                                              \
+  combine_bwd_kernel<DT, V, GW><<<grid, cfg.threads, 0, s>>>(                                   \
+      pv.seg_off, pv.row_of_slot, pv.src_sorted, pv.w_sorted, grad_out, grad_out_row_stride,    \
+      grad_rows, grad_w, T, D, dvec, cfg.tiles)
+  FMOE_DISPATCH_DTYPE(dtype, DT, {
+    if (grad_w) FMOE_BWD_LAUNCH(DT, 1, true); else FMOE_BWD_LAUNCH(DT, 1, false);
+    rc = check_launch("combine_bwd_kernel");
+  });
+#undef FMOE_BWD_LAUNCH
+  return rc;
+}
+
+extern "C" int fmoe_permute_fwd(const void* x, int64_t x_row_stride, const int32_t* slot_of,
+                                void* permuted, int64_t T, int64_t K, int64_t D, int dtype,
+                                void* stream) {
+  FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_permute_fwd: bad dtype %d", dtype);
+  FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_permute_fwd: negative size");
+  FMOE_REQUIRE(T * K < (1ll << 31), FMOE_ERR_UNSUPPORTED, "fmoe_permute_fwd: T*K must fit in int32");
+  if (T == 0 || K == 0 || D == 0) return FMOE_OK;
+  FMOE_REQUIRE(x && slot_of && permuted, FMOE_ERR_ARG, "fmoe_permute_fwd: null pointer argument");
+  FMOE_REQUIRE(x_row_stride >= D, FMOE_ERR_ARG, "fmoe_permute_fwd: x_row_stride < D");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int eb = dtype_size(dtype);
+  const int kvec = 16 / eb;
+  const bool vec_ok = D % kvec == 0 && aligned_to(x, 16) && aligned_to(permuted, 16) &&
+                      (x_row_stride * eb) % 16 == 0;
+  int rc = 0;
+  if (!vec_ok) {
+    const int64_t blocks = (T * K * D + 255) / 256;
+    const int grid = static_cast<int>(blocks < kNumSMs * 16 ? blocks : kNumSMs * 16);
+    FMOE_DISPATCH_DTYPE(dtype, DT, {
+      permute_fwd_scalar_kernel<DT><<<grid, 256, 0, s>>>(x, x_row_stride, slot_of, permuted, T,
+                                                         static_cast<int>(K), D);
+      rc = check_launch("permute_fwd_scalar_kernel");
+    });
+    return rc;
+  }
+  const int64_t dvec = D / kvec;
+  const TileCfg cfg = pick_tile(dvec, g_gather_v > 0 ? g_gather_v : 2, g_gather_threads);
+  const int grid = static_cast<int>(clamp_grid(T * cfg.tiles, g_gather_ctas_per_sm));
+#define FMOE_PERM_LAUNCH(DT, V)                                                            \
+  permute_fwd_kernel<DT, V><<<grid, cfg.threads, 0, s>>>(x, x_row_stride, slot_of, permuted, T, \
+                                                         static_cast<int>(K), D, dvec, cfg.tiles)
+  FMOE_DISPATCH_DTYPE(dtype, DT, {
+    if (cfg.v == 1) FMOE_PERM_LAUNCH(DT, 1);
+    else if (cfg.v == 2) FMOE_PERM_LAUNCH(DT, 2);
+    else FMOE_PERM_LAUNCH(DT, 4);
+    rc = check_launch("permute_fwd_kernel");
+  });
+#undef FMOE_PERM_LAUNCH
+  return rc;
+}
+
+extern "C" int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_of, void* grad_x,
+                                int64_t grad_x_row_stride, int64_t T, int64_t K, int64_t D,
+                                int dtype, void* stream) {
+  FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_permute_bwd: bad dtype %d", dtype);
+  FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_permute_bwd: negative size");
+  FMOE_REQUIRE(T * K < (1ll << 31), FMOE_ERR_UNSUPPORTED, "fmoe_permute_bwd: T*K must fit in int32");
+  if (T == 0 || D == 0) return FMOE_OK;
+  FMOE_REQUIRE(grad_x != nullptr, FMOE_ERR_ARG, "fmoe_permute_bwd: grad_x is null");
+  FMOE_REQUIRE(K == 0 || (grad_permuted && slot_of), FMOE_ERR_ARG,
+               "fmoe_permute_bwd: null pointer argument");
+  FMOE_REQUIRE(grad_x_row_stride >= D, FMOE_ERR_ARG, "fmoe_permute_bwd: grad_x_row_stride < D");
+  const SlotSource src{slot_of, static_cast<const char*>(grad_permuted),
+                       D * static_cast<int64_t>(dtype_size(dtype)), T * K, static_cast<int>(K)};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = 0;
+  FMOE_DISPATCH_DTYPE(dtype, DT,
+                      rc = (launch_gather_sum<DT, false, SlotSource>(src, grad_x, grad_x_row_stride,
+                                                                     T, D, 0, s)));
+  return rc;
+}

@@ -1,0 +1,324 @@
+"""Grouped pointer-table combine: the operator layer of polkadot21/fastmoe on B200.
+
+Same public names, argument order and semantics as the reference module
+`src/fastmoe/kernels/ops.py`:
+
+  grouped_weighted_scatter_add (ops.py:365-394), weighted_scatter_add (ops.py:397),
+  prepare_grouped_metadata (ops.py:200-271), GroupedWeightedScatterAdd (ops.py:316-359)
+
+Behind them sit hand-written sm_100a CUDA kernels reached through the C ABI of
+`libfastmoe_b200.so`. There is no Triton and no CPU path: CPU tensors raise.
+
+Differences from the reference that a caller can observe:
+  * the gate weights receive a gradient (the reference's CUDA backward returns
+    None for them, ops.py:358-359; its CPU path produces one through autograd);
+  * arguments are validated and bad ones raise ValueError before any launch;
+  * results are bit-reproducible from run to run in the default "gather" mode.
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .. import _lib
+
+__all__ = [
+    "grouped_weighted_scatter_add",
+    "weighted_scatter_add",
+    "prepare_grouped_metadata",
+    "GroupedWeightedScatterAdd",
+    "GroupedMetadata",
+    "CombinePlan",
+    "build_combine_plan",
+    "combine_mode",
+    "set_combine_mode",
+    "read_status",
+    "HAS_TRITON",
+]
+
+# The reference exports this flag (ops.py:10,12); this build never uses Triton.
+HAS_TRITON = False
+
+_DTYPES = {torch.float32: _lib.FMOE_F32, torch.bfloat16: _lib.FMOE_BF16, torch.float16: _lib.FMOE_F16}
+_ITYPES = {torch.int64: _lib.FMOE_I64, torch.int32: _lib.FMOE_I32}
+
+# "gather": plan (inverse map) + token-major gather, one write per output element.
+# "scatter": one launch with vector red.global.add, no scratch memory.
+_mode = os.environ.get("FASTMOE_B200_COMBINE", "gather")
+_check = os.environ.get("FASTMOE_B200_CHECK", "0") == "1"
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def combine_mode() -> str:
+    return _mode
+
+
+def set_combine_mode(mode: str) -> None:
+    """Selects the combine algorithm: "gather" (default) or "scatter"."""
+    global _mode
+    if mode not in ("gather", "scatter"):
+        raise ValueError(f"combine mode must be 'gather' or 'scatter', got {mode!r}")
+    _mode = mode
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """One int32 per device that kernels OR error bits into (bad index, null pointer ...)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(key)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = word
+    return word
+
+
+def read_status(device=None, reset: bool = True) -> int:
+    """Reads (synchronising) and optionally clears the device status word.
+
+    Non-zero means a kernel skipped rows: bit 1 = index outside [0, T),
+    bit 2 = row outside its expert, bit 4 = null pointer-table entry.
+    """
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(device)
+    value = int(word.item())
+    if reset and value:
+        word.zero_()
+    return value
+
+
+def _maybe_check(device: torch.device, what: str) -> None:
+    if _check:
+        value = read_status(device)
+        if value:
+            raise RuntimeError(f"{what}: device status word = {value} (rows were skipped)")
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"fastmoe_b200 has no CPU path: `{name}` lives on {t.device}; move it to a CUDA device"
+        )
+
+
+class GroupedMetadata(tuple):
+    """The reference's 5-tuple (ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts)
+    (ops.py:271) plus `num_rows` (the sum of the chunk sizes) as an attribute."""
+
+    num_rows: int
+
+    def __new__(cls, ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts, num_rows):
+        self = super().__new__(cls, (ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts))
+        self.num_rows = num_rows
+        return self
+
+
+def prepare_grouped_metadata(expert_tensors, device):
+    """Pointer table, per-expert row counts and their exclusive prefix sum.
+
+    Same result as the reference (ops.py:200-271): `ptr_table` int64 [E] of raw
+    addresses, `chunk_sizes` int32 [E], `expert_offsets` int64 [E], and the Python
+    ints `max_rows` and `num_experts`. The table borrows the addresses: it is valid
+    only while the same tensors stay alive at the same place. All three arrays
+    travel in one host-to-device copy.
+    """
+    sizes = [int(t.shape[0]) for t in expert_tensors]
+    num_experts = len(sizes)
+    offsets, run = [], 0
+    for s in sizes:
+        offsets.append(run)
+        run += s
+    ptrs = [t.data_ptr() for t in expert_tensors]
+    packed = torch.tensor(ptrs + offsets + sizes, dtype=torch.int64).to(device)
+    ptr_table = packed[:num_experts]
+    expert_offsets = packed[num_experts : 2 * num_experts]
+    chunk_sizes = packed[2 * num_experts :].to(torch.int32)
+    max_rows = max(sizes) if sizes else 0
+    return GroupedMetadata(ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts, run)
+
+
+def _normalise_experts(expert_tensors):
+    """Checks the expert matrices and returns them row-major contiguous."""
+    if len(expert_tensors) == 0:
+        raise ValueError("expert_tensors is empty")
+    ref = expert_tensors[0]
+    if ref.dim() != 2:
+        raise ValueError(f"expert tensors must be 2-D [rows, D], got shape {tuple(ref.shape)}")
+    if ref.dtype not in _DTYPES:
+        raise ValueError(f"unsupported expert dtype {ref.dtype}; use float32, bfloat16 or float16")
+    out = []
+    for i, t in enumerate(expert_tensors):
+        _require_cuda(t, f"expert_tensors[{i}]")
+        if t.dim() != 2 or t.shape[1] != ref.shape[1]:
+            raise ValueError(
+                f"expert_tensors[{i}] has shape {tuple(t.shape)}, expected [rows, {ref.shape[1]}]"
+            )
+        if t.dtype != ref.dtype or t.device != ref.device:
+            raise ValueError(f"expert_tensors[{i}] differs in dtype or device from expert_tensors[0]")
+        # the kernels read rows at stride D, as the reference kernel does (ops.py:138)
+        out.append(t if t.is_contiguous() else t.contiguous())
+    return out
+
+
+def _check_routing(indices, weights, n_rows):
+    _require_cuda(indices, "indices")
+    _require_cuda(weights, "weights")
+    if indices.dtype not in _ITYPES:
+        raise ValueError(f"indices must be int64 or int32, got {indices.dtype}")
+    if weights.dtype not in _DTYPES:
+        raise ValueError(f"unsupported weights dtype {weights.dtype}")
+    if indices.dim() != 1 or weights.dim() != 1:
+        raise ValueError("indices and weights must be 1-D")
+    if indices.shape[0] != n_rows or weights.shape[0] != n_rows:
+        raise ValueError(
+            f"indices ({indices.shape[0]}) and weights ({weights.shape[0]}) must have one entry per "
+            f"expert row ({n_rows})"
+        )
+    return indices.contiguous(), weights.contiguous()
+
+
+class CombinePlan:
+    """Device-side inverse of `indices`: per output row, its source rows in ascending
+    global row order with resolved addresses and fp32 weights. Holds references to
+    everything the stored addresses point into."""
+
+    def __init__(self, buf, n_rows, n_out, dim, dtype, keepalive):
+        self.buf, self.n_rows, self.n_out, self.dim, self.dtype = buf, n_rows, n_out, dim, dtype
+        self._keepalive = keepalive
+
+
+def build_combine_plan(expert_tensors, indices, weights, n_out, metadata=None) -> CombinePlan:
+    """Builds the plan for out[n_out, D]. Four small launches on the current stream."""
+    experts = _normalise_experts(expert_tensors)
+    ref = experts[0]
+    if metadata is None:
+        metadata = prepare_grouped_metadata(experts, ref.device)
+    ptr_table, chunk_sizes, expert_offsets, _, num_experts = metadata
+    n_rows = sum(int(t.shape[0]) for t in experts)
+    indices, weights = _check_routing(indices, weights, n_rows)
+    dim = int(ref.shape[1])
+    nbytes = _lib.lib().fmoe_combine_plan_bytes(n_rows, n_out)
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=ref.device)
+    _lib.call(
+        "fmoe_combine_plan",
+        ptr_table.data_ptr(), chunk_sizes.data_ptr(), expert_offsets.data_ptr(),
+        indices.data_ptr(), _ITYPES[indices.dtype], weights.data_ptr(), _DTYPES[weights.dtype],
+        num_experts, n_rows, n_out, dim, _DTYPES[ref.dtype],
+        buf.data_ptr(), nbytes, _status_word(ref.device).data_ptr(), _stream_ptr(ref.device),
+    )  # fmt: skip
+    return CombinePlan(buf, n_rows, n_out, dim, ref.dtype, (experts, metadata, indices, weights))
+
+
+def _check_out(out, ref, what="out"):
+    _require_cuda(out, what)
+    if out.dim() != 2 or out.shape[1] != ref.shape[1]:
+        raise ValueError(f"{what} must be [T, {ref.shape[1]}], got {tuple(out.shape)}")
+    if out.dtype != ref.dtype:
+        raise ValueError(f"{what} dtype {out.dtype} differs from the expert dtype {ref.dtype}")
+    if out.shape[1] > 1 and out.stride(1) != 1:
+        raise ValueError(f"{what} must have unit column stride")
+
+
+def _combine_into(expert_tensors, indices, weights, out, metadata, accumulate, mode=None):
+    """Runs the combine into `out` ([T, D], any row stride). Returns the plan (or None)."""
+    mode = _mode if mode is None else mode
+    experts = _normalise_experts(expert_tensors)
+    ref = experts[0]
+    _check_out(out, ref)
+    n_out, dim = int(out.shape[0]), int(out.shape[1])
+    row_stride = int(out.stride(0)) if n_out > 1 else dim
+    if mode == "gather":
+        plan = build_combine_plan(experts, indices, weights, n_out, metadata)
+        _lib.call(
+            "fmoe_combine_gather", plan.buf.data_ptr(), out.data_ptr(), row_stride, plan.n_rows,
+            n_out, dim, _DTYPES[ref.dtype], 1 if accumulate else 0, _stream_ptr(ref.device),
+        )  # fmt: skip
+        _maybe_check(ref.device, "grouped_weighted_scatter_add")
+        return plan
+    if metadata is None:
+        metadata = prepare_grouped_metadata(experts, ref.device)
+    ptr_table, chunk_sizes, expert_offsets, _, num_experts = metadata
+    n_rows = sum(int(t.shape[0]) for t in experts)
+    indices, weights = _check_routing(indices, weights, n_rows)
+    if not accumulate:
+        out.zero_()
+    _lib.call(
+        "fmoe_combine_scatter",
+        ptr_table.data_ptr(), chunk_sizes.data_ptr(), expert_offsets.data_ptr(),
+        indices.data_ptr(), _ITYPES[indices.dtype], weights.data_ptr(), _DTYPES[weights.dtype],
+        out.data_ptr(), row_stride, num_experts, n_rows, n_out, dim, _DTYPES[ref.dtype],
+        _status_word(ref.device).data_ptr(), _stream_ptr(ref.device),
+    )  # fmt: skip
+    _maybe_check(ref.device, "grouped_weighted_scatter_add")
+    return None
+
+
+class GroupedWeightedScatterAdd(torch.autograd.Function):
+    """out[indices[g]] += expert_row_g * weights[g] with gradients for the expert rows
+    and the gate weights. Argument order as in the reference (ops.py:318):
+    (indices, weights, out_shape, *expert_tensors)."""
+
+    @staticmethod
+    def forward(ctx, indices, weights, out_shape, *expert_tensors):
+        experts = _normalise_experts(expert_tensors)
+        ref = experts[0]
+        out_shape = tuple(int(s) for s in out_shape)
+        if len(out_shape) != 2:
+            raise ValueError(f"out_shape must be (T, D), got {out_shape}")
+        # every row is written by the gather kernel, so no zero-fill pass is needed
+        out = torch.empty(out_shape, device=ref.device, dtype=ref.dtype)
+        plan = _combine_into(experts, indices, weights, out, None, accumulate=False, mode="gather")
+        ctx.plan = plan
+        ctx.save_for_backward(indices, weights, *expert_tensors)
+        ctx.expert_sizes = [int(t.shape[0]) for t in experts]
+        ctx.weights_dtype = weights.dtype
+        ctx.dim = out_shape[1]
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        plan = ctx.plan
+        n_rows, dim = plan.n_rows, ctx.dim
+        if grad_output.dim() != 2 or (dim > 1 and grad_output.stride(1) != 1):
+            grad_output = grad_output.contiguous()
+        if grad_output.dtype != plan.dtype:
+            grad_output = grad_output.to(plan.dtype)
+        device = grad_output.device
+        grad_rows = torch.empty(n_rows, dim, device=device, dtype=plan.dtype)
+        want_gw = ctx.needs_input_grad[1]
+        grad_w = torch.empty(n_rows, device=device, dtype=torch.float32) if want_gw else None
+        row_stride = int(grad_output.stride(0)) if grad_output.shape[0] > 1 else dim
+        _lib.call(
+            "fmoe_combine_bwd", plan.buf.data_ptr(), grad_output.data_ptr(), row_stride,
+            grad_rows.data_ptr(), grad_w.data_ptr() if want_gw else None, n_rows, plan.n_out, dim,
+            _DTYPES[plan.dtype], _stream_ptr(device),
+        )  # fmt: skip
+        grad_experts = torch.split(grad_rows, ctx.expert_sizes)
+        if want_gw:
+            grad_w = grad_w.to(ctx.weights_dtype)
+        return None, grad_w, None, *grad_experts
+
+
+def grouped_weighted_scatter_add(expert_tensors, indices, weights, out_shape, out=None, metadata=None):
+    """Sums weighted rows of disjoint per-expert matrices into token rows.
+
+    Same contract as the reference (ops.py:365-394): with `out` given, rows are
+    accumulated into it in place (no autograd, no zero-fill, graph-capturable with
+    cached `metadata`); otherwise a fresh tensor in the experts' dtype is returned
+    through autograd.
+    """
+    _require_cuda(indices, "indices")
+    if out is not None:
+        _combine_into(expert_tensors, indices, weights, out, metadata, accumulate=True)
+        return out
+    return GroupedWeightedScatterAdd.apply(indices, weights, out_shape, *expert_tensors)
+
+
+def weighted_scatter_add(src, indices, weights, out_shape, out=None):
+    """Single-matrix form (ops.py:397-398)."""
+    return grouped_weighted_scatter_add([src], indices, weights, out_shape, out)

@@ -1,0 +1,210 @@
+/*
+ * fastmoe_b200 — C ABI of the B200 (sm_100a) MoE dispatch/combine hot path.
+ *
+ * Every entry point takes plain device pointers, 64-bit sizes and an opaque
+ * CUDA stream handle (a cudaStream_t passed as void*; NULL = the legacy default
+ * stream). Nothing here depends on PyTorch. The library is loaded with dlopen /
+ * ctypes / cgo / JNI alike.
+ *
+ * Return value of every function that returns int:
+ *    0   success
+ *   <0   argument error (FMOE_ERR_*), nothing was launched
+ *   >0   a cudaError_t raised by a launch or a copy
+ * fmoe_last_error() gives a human-readable message for the calling thread.
+ *
+ * None of the device entry points allocates, frees or synchronises unless its
+ * comment says so: they only enqueue work on `stream`, so they may be captured
+ * in a CUDA graph. Scratch memory is always passed in by the caller
+ * (`fmoe_*_bytes` tells how much).
+ *
+ * Reference interface citations are paths inside polkadot21/fastmoe.
+ */
+#ifndef FASTMOE_B200_H
+#define FASTMOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define FMOE_OK 0
+#define FMOE_ERR_ARG (-1)         /* null pointer, negative size, bad enum       */
+#define FMOE_ERR_UNSUPPORTED (-2) /* valid request this build does not serve      */
+#define FMOE_ERR_WORKSPACE (-3)   /* workspace missing, misaligned or too small   */
+#define FMOE_ERR_DEVICE (-4)      /* wrong GPU architecture / no device           */
+
+/* element types of the payload ([rows, D] matrices) and of the gate weights */
+#define FMOE_F32 0
+#define FMOE_BF16 1
+#define FMOE_F16 2
+/* integer types of the index vector */
+#define FMOE_I64 0
+#define FMOE_I32 1
+
+/* bits of the device status word (int32, caller-allocated, optional).
+ * Kernels OR bits into it and skip the offending row; they never trap.      */
+#define FMOE_STATUS_BAD_INDEX 1   /* a target index outside [0, T)            */
+#define FMOE_STATUS_BAD_EXPERT 2  /* an expert id outside [0, E)              */
+#define FMOE_STATUS_NULL_PTR 4    /* a null entry in the pointer table        */
+#define FMOE_STATUS_WAIT_TIMEOUT 8 /* a bounded device-side wait gave up      */
+
+/* ---- library ------------------------------------------------------------ */
+
+/* ABI version, bumped on any signature change. */
+int fmoe_abi_version(void);
+/* Message of the last failing call on this thread ("" if none). */
+const char* fmoe_last_error(void);
+/* Name of a status code returned by this library. */
+const char* fmoe_status_name(int status);
+
+/* Launch-shape knobs for benchmark sweeps; process-wide, not thread-safe against
+ * concurrent launches. Keys: "gather_v" (16-byte vectors per thread: 0 = auto,
+ * 1, 2, 4), "gather_threads" (threads per CTA, 0 = auto, else a multiple of 32
+ * up to 256), "gather_ctas_per_sm" (0 = one CTA per work item, else a
+ * persistent grid of 148 x value CTAs), "bwd_ctas_per_sm". */
+int fmoe_tune(const char* key, int value);
+
+/* ---- combine: scatter form ---------------------------------------------- */
+/*
+ * out[idx[g], :] += src_e[r, :] * w[g]   for g = expert_offsets[e] + r,
+ * r < chunk_sizes[e], src_e = (T*)ptr_table[e] with row stride D.
+ *
+ * Replaces the Triton kernel `_grouped_weighted_scatter_add_kernel`
+ * (src/fastmoe/kernels/ops.py:57-194) and its launcher
+ * `_launch_grouped_kernel` (ops.py:277-310). One launch over the flattened
+ * (expert,row) space; consecutive rows that share a target are summed in fp32
+ * registers before one vector `red.global.add` per 16 bytes. Needs no scratch.
+ * `out` is accumulated into (never zeroed), as in the reference (ops.py:389-390).
+ * Adds land in `out`'s type, so bf16/f16 results depend on the arrival order.
+ *
+ * ptr_table      int64[E]  device: addresses of the E expert matrices
+ * chunk_sizes    int32[E]  device: rows of each expert matrix
+ * expert_offsets int64[E]  device: exclusive prefix sum of chunk_sizes
+ * idx            [N] device, idx_type FMOE_I64|FMOE_I32: target row in out
+ * w              [N] device, w_dtype: gate weight per row
+ * out            [T, D] device, dtype, row stride out_row_stride (elements)
+ * status         optional int32* device status word
+ */
+int fmoe_combine_scatter(const int64_t* ptr_table, const int32_t* chunk_sizes,
+                         const int64_t* expert_offsets, const void* idx, int idx_type,
+                         const void* w, int w_dtype, void* out, int64_t out_row_stride,
+                         int64_t E, int64_t N, int64_t T, int64_t D, int dtype,
+                         int32_t* status, void* stream);
+
+/* ---- combine: planned (token-major gather) form ------------------------- */
+/*
+ * The fast path. A plan is the inverse of `idx`: for every output row t the
+ * list of source rows that target it, in ascending global row order (the order
+ * in which the reference's CPU loop adds them, ops.py:373-384), already
+ * resolved through the pointer table to a source address and an fp32 gate
+ * weight. With the plan, one CTA owns an output row tile, pulls its source
+ * rows with 16-byte loads, accumulates in fp32 registers in that fixed order
+ * and writes each output element exactly once: no atomics, no zero-fill pass,
+ * bit-reproducible from run to run.
+ *
+ * The plan lives in caller-provided scratch of fmoe_combine_plan_bytes(N, T)
+ * bytes, 256-byte aligned. It stays valid while idx, w, the pointer table and
+ * the expert matrices are unchanged; forward and backward share it.
+ */
+size_t fmoe_combine_plan_bytes(int64_t N, int64_t T);
+
+/* Builds the plan. Replaces `prepare_grouped_metadata`'s device side
+ * (ops.py:200-271) plus the per-row lookups of the Triton kernel
+ * (ops.py:129-163). Four small launches, no host synchronisation. */
+int fmoe_combine_plan(const int64_t* ptr_table, const int32_t* chunk_sizes,
+                      const int64_t* expert_offsets, const void* idx, int idx_type,
+                      const void* w, int w_dtype, int64_t E, int64_t N, int64_t T,
+                      int64_t D, int dtype, void* plan, size_t plan_bytes,
+                      int32_t* status, void* stream);
+
+/* out[t,:] (=|+=) sum over the plan's rows of t, in plan order, of row*w.
+ * accumulate=0 overwrites every row of out (rows without sources become 0):
+ * the `GroupedWeightedScatterAdd.forward` semantics (ops.py:318-331) without
+ * the torch.zeros pass. accumulate=1 adds to out: the `out=` semantics
+ * (ops.py:389-390). */
+int fmoe_combine_gather(const void* plan, void* out, int64_t out_row_stride, int64_t N,
+                        int64_t T, int64_t D, int dtype, int accumulate, void* stream);
+
+/*
+ * Backward of the combine (replaces `GroupedWeightedScatterAdd.backward`,
+ * ops.py:334-359, and adds the gate gradient the reference leaves out at
+ * ops.py:358-359; the reference's CPU path produces it through autograd):
+ *   grad_rows[g, :] = grad_out[idx[g], :] * w[g]           ([N, D], dtype)
+ *   grad_w[g]       = sum_c grad_out[idx[g], c] * src_g[c]  (fp32, optional)
+ * grad_out is read once per output row; grad_w may be NULL.
+ */
+int fmoe_combine_bwd(const void* plan, const void* grad_out, int64_t grad_out_row_stride,
+                     void* grad_rows, float* grad_w, int64_t N, int64_t T, int64_t D,
+                     int dtype, void* stream);
+
+/* ---- router: top-k + gate softmax ---------------------------------------- */
+/*
+ * Per token: the K largest of E logits in descending order (ties: lower expert
+ * id first), then softmax over those K values in fp32, rounded to w_dtype.
+ * Replaces torch.topk + F.softmax in `MoEFeedForward.gate_and_sort`
+ * (src/fastmoe/models/tiny_model.py:97-100).
+ * logits [T, E] dtype; topk_idx int64 [T, K]; topk_w [T, K] w_dtype.
+ */
+int fmoe_route_topk(const void* logits, int dtype, int64_t T, int64_t E, int64_t K,
+                    int64_t* topk_idx, void* topk_w, int w_dtype, void* stream);
+
+/* ---- index / offset builder ---------------------------------------------- */
+/*
+ * Stable counting sort of the T*K routed slots by expert id (ties by flat
+ * position t*K+k), replacing argsort + gathers + bincount
+ * (tiny_model.py:105-153):
+ *   reverse_map[i]  int64[N]  token of sorted slot i
+ *   sorted_w[i]     [N] w_dtype gate weight of sorted slot i
+ *   counts[e]       int64[E]  rows per expert (torch.bincount)
+ *   offsets[e]      int64[E]  exclusive prefix sum of counts
+ *   rank_counts[r]  int64[world] rows per owning rank (E/world experts each)
+ *   slot_of[t*K+k]  int32[N]  sorted position of routed slot (t,k): the
+ *                   inverse map that the permute and the combine consume
+ * scratch: fmoe_build_index_bytes(T, E, K) bytes, 256-byte aligned.
+ */
+size_t fmoe_build_index_bytes(int64_t T, int64_t E, int64_t K);
+int fmoe_build_index(const int64_t* topk_idx, const void* topk_w, int w_dtype, int64_t T,
+                     int64_t E, int64_t K, int64_t world, int64_t* reverse_map,
+                     void* sorted_w, int64_t* counts, int64_t* offsets,
+                     int64_t* rank_counts, int32_t* slot_of, void* scratch,
+                     size_t scratch_bytes, int32_t* status, void* stream);
+
+/* ---- dispatch permute ------------------------------------------------------ */
+/*
+ * permuted[slot_of[t*K+k], :] = x[t, :]   (tiny_model.py:133, `x_flat[rev]`),
+ * token-major: each row of x is read once and written K times.
+ */
+int fmoe_permute_fwd(const void* x, int64_t x_row_stride, const int32_t* slot_of,
+                     void* permuted, int64_t T, int64_t K, int64_t D, int dtype,
+                     void* stream);
+/* grad_x[t, :] = sum_k grad_permuted[slot_of[t*K+k], :] in fp32, ascending k
+ * (the index_put(accumulate) that autograd runs for tiny_model.py:133). */
+int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_of, void* grad_x,
+                     int64_t grad_x_row_stride, int64_t T, int64_t K, int64_t D,
+                     int dtype, void* stream);
+
+/* ---- host-buffer call -------------------------------------------------------- */
+/*
+ * The whole combine for a caller that holds HOST memory: copies the E expert
+ * matrices, idx and w into `arena` (device scratch of at least
+ * fmoe_combine_host_arena_bytes(...) bytes, caller-allocated), builds the
+ * pointer table and the plan there, runs the gather and copies out[T, D] back
+ * to `out_host`. Host buffers should be pinned for full PCIe speed. The call
+ * returns after the stream has drained (it synchronises `stream`).
+ * Mirrors `grouped_weighted_scatter_add(expert_tensors, indices, weights,
+ * out_shape)` (ops.py:365-394) for host callers.
+ */
+size_t fmoe_combine_host_arena_bytes(const int64_t* chunk_sizes_host, int64_t E, int64_t N,
+                                     int64_t T, int64_t D, int dtype);
+int fmoe_combine_host(const void* const* expert_rows_host, const int64_t* chunk_sizes_host,
+                      const void* idx_host, int idx_type, const void* w_host, int w_dtype,
+                      void* out_host, int64_t E, int64_t N, int64_t T, int64_t D, int dtype,
+                      void* arena, size_t arena_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTMOE_B200_H */
