@@ -1,0 +1,391 @@
+"""Benchmark of the grouped pointer-table combine (the MoE hot path's dominant kernel).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one full combine of one synthetic batch through the public operator
+`grouped_weighted_scatter_add(expert_tensors, indices, weights, out_shape)`:
+plan build (inverse map, 4 small kernels) + token-major gather kernel, output
+freshly produced. The default workload is the combine microbenchmark
+(T=8192 tokens, D=16384, E=256 experts, top-8, bf16; 256 disjoint expert output
+matrices, 2.15 GB of rows, which exceeds the 126 MB L2, so every step streams
+from HBM).
+
+Rank 0 prints ONE JSON line. Keys beyond the usual ones:
+  value     whole-job GB/s of algorithmic bytes, inputs resident in HBM
+  e2e       the same metric through the C-ABI host-buffer call fmoe_combine_host
+            (pinned host inputs -> device -> combine -> host), copies timed
+  roofline  the gather kernel alone: algorithmic bytes / its CUDA-event time,
+            against the measured HBM copy bandwidth of this GPU pool
+  cpu_baseline  the CPU restatement of the reference's path (oracle/), all host
+            threads, timed in this run on the same workload
+
+With --gpus N > 1 (under torchrun) every rank runs an independent replica of the
+workload: the combine has no cross-GPU step ("replicas only"); the aggregate is
+the sum over ranks divided by the slowest rank's time.
+
+`--impl reference` times the reference's CPU implementation of the path (the
+oracle port; the reference is pure Python over torch and has nothing to compile)
+on the box's host cores, same workload, same metric.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "combine_hbm_gbs"
+UNIT = "GB/s"
+
+WORKLOADS = {
+    # name: (T, D, E, K, routing)
+    "combine_cfg2_bf16_T8192_D16384_E256_top8": (8192, 16384, 256, 8, "softmax"),
+    "combine_cfg3_zipf_bf16_T8192_D16384_E256_top8": (8192, 16384, 256, 8, "zipf"),
+    "combine_small_bf16_T1024_D4096_E64_top8": (1024, 4096, 64, 8, "softmax"),
+}
+DEFAULT_WORKLOAD = "combine_cfg2_bf16_T8192_D16384_E256_top8"
+
+# DRAM bytes (read + write) of one gather launch on the default workload, from the
+# ncu capture summarised in profiles/combine_gather_cfg2.md; None until captured.
+NCU_TRAFFIC_BYTES = {DEFAULT_WORKLOAD: None}
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.05):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        return {
+            "sm_mhz": statistics.median(self.samples),
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def host_copy(wl):
+    """Pinned host copies of the workload (bf16 rows as uint16 bit patterns for numpy)."""
+    import torch
+
+    experts = [torch.empty(e.shape, dtype=e.dtype).pin_memory() for e in wl.experts]
+    for h, d in zip(experts, wl.experts):
+        h.copy_(d)
+    idx = wl.indices.cpu().pin_memory()
+    w = wl.weights.cpu().pin_memory()
+    torch.cuda.synchronize()
+    return experts, idx, w
+
+
+def cpu_pass(host, T, D):
+    """One combine on the host cores with the reference's bf16 CPU arithmetic (oracle port)."""
+    import numpy as np
+    import torch
+
+    import oracle
+
+    experts, idx, w = host
+    ex = [e.view(torch.int16).numpy().view(np.uint16) for e in experts]
+    t0 = time.perf_counter()
+    oracle.combine_bf16(ex, idx.numpy(), w.view(torch.int16).numpy().view(np.uint16), T)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank):
+    """The reference arm: the CPU path (oracle port) on this box's host cores."""
+    if rank != 0:
+        return
+    import torch
+
+    import oracle
+    from fastmoe_b200.workloads import make_combine_workload
+
+    T, D, E, K, routing = WORKLOADS[args.workload]
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    wl = make_combine_workload(T, D, E, K, torch.bfloat16, routing, seed=0, device=device)
+    if device == "cuda":
+        host = host_copy(wl)
+    else:
+        host = (wl.experts, wl.indices, wl.weights)
+    nbytes = wl.algorithmic_bytes()
+    del wl
+    for _ in range(args.warmup):
+        cpu_pass(host, T, D)
+    t = [cpu_pass(host, T, D) for _ in range(args.steps)]
+    total = sum(t)
+    value = nbytes * args.steps / total / 1e9
+    cores = oracle.num_threads()
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": total / args.steps * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "T": T, "D": D, "E": E, "top_k": K, "routing": routing},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "the full workload, every step one complete combine on the host"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    from fastmoe_b200 import _lib
+    from fastmoe_b200.kernels import ops
+    from fastmoe_b200.workloads import make_combine_workload
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    _lib.lib()  # fail now if the CUDA library is missing
+
+    T, D, E, K, routing = WORKLOADS[args.workload]
+    wl = make_combine_workload(T, D, E, K, torch.bfloat16, routing, seed=rank, device=device)
+    nbytes = wl.algorithmic_bytes()
+    shape = (T, D)
+
+    def step():
+        return ops.grouped_weighted_scatter_add(wl.experts, wl.indices, wl.weights, shape)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    barrier()
+
+    ops.kernel_events = []  # (start, end) CUDA events around every gather launch
+    launches0 = ops.launch_count
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            out = step()
+        end.record()
+        barrier()
+    elapsed_ms = start.elapsed_time(end)
+    gather_ms = [s.elapsed_time(e) for s, e in ops.kernel_events]
+    launches = ops.launch_count - launches0
+    ops.kernel_events = None
+    assert ops.read_status(device) == 0, "kernels flagged skipped rows"
+    checksum = float(out.float().abs().mean())
+    assert checksum > 0.0
+
+    # ---- end to end through the C ABI with host buffers ----------------------------
+    host = host_copy(wl)
+    hex_, hidx, hw = host
+    import ctypes
+
+    lib = _lib.lib()
+    sizes = (ctypes.c_int64 * E)(*wl.counts)
+    ptrs = (ctypes.c_void_p * E)(*[h.data_ptr() for h in hex_])
+    arena_bytes = lib.fmoe_combine_host_arena_bytes(sizes, E, wl.N, T, D, _lib.FMOE_BF16)
+    arena = torch.empty(arena_bytes, dtype=torch.uint8, device=device)
+    out_host = torch.empty(T, D, dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.current_stream().cuda_stream
+    h2d = sum(h.numel() * h.element_size() for h in hex_) + hidx.numel() * 8 + hw.numel() * 2
+    d2h = out_host.numel() * 2
+
+    def e2e_step():
+        _lib.call("fmoe_combine_host", ptrs, sizes, hidx.data_ptr(), _lib.FMOE_I64, hw.data_ptr(),
+                  _lib.FMOE_BF16, out_host.data_ptr(), E, wl.N, T, D, _lib.FMOE_BF16,
+                  arena.data_ptr(), arena_bytes, stream)  # fmt: skip
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()  # returns after its stream has drained
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    assert torch.equal(out_host.to(device), out), "host-buffer call and device call disagree"
+
+    # ---- aggregate over ranks -------------------------------------------------------
+    stats = torch.tensor([elapsed_ms, e2e_s], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_s = stats.tolist()
+    value = nbytes * world * args.steps / (elapsed_ms / 1e3) / 1e9
+    e2e_value = nbytes * world * e2e_steps / e2e_s / 1e9
+
+    if rank != 0:
+        return
+
+    peak, peak_kind = measured_peak()
+    kernel_ms = statistics.mean(gather_ms) if gather_ms else None
+    achieved = nbytes / (kernel_ms / 1e3) / 1e9 if kernel_ms else None
+    roofline = {
+        "bound": "hbm",
+        "kernel": "gather_sum_kernel (combine forward)",
+        "achieved": achieved,
+        "peak": peak,
+        "peak_kind": peak_kind,
+        "unit": "GB/s",
+        "frac": achieved / peak if achieved else None,
+        "frac_of_8TBs_spec": achieved / 8000.0 if achieved else None,
+        "kernel_ms": kernel_ms,
+        "algorithmic_bytes": nbytes,
+        "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+    }
+
+    # CPU baseline: the oracle port on this box's cores, whole workload, a few passes
+    import oracle
+
+    cpu_pass(host, T, D)
+    cpu_t = [cpu_pass(host, T, D) for _ in range(3)]
+    cpu_baseline = {
+        "value": nbytes / statistics.median(cpu_t) / 1e9,
+        "unit": UNIT,
+        "cores": oracle.num_threads(),
+        "kind": "port",
+        "sample": "the full workload, median of 3 complete combines after 1 warm-up",
+        "ms": statistics.median(cpu_t) * 1e3,
+    }
+
+    line = {
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": elapsed_ms / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": args.workload, "T": T, "D": D, "E": E, "top_k": K, "routing": routing,
+            "rows": wl.N, "l2": "inputs (2.15 GB) exceed the 126 MB L2; no flush needed",
+            "multi_gpu": "replicas only",
+        },
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps, "call": "fmoe_combine_host (C ABI, pinned host buffers)"},
+        "gpu_launches": launches,
+        "roofline": roofline,
+        "cpu_baseline": cpu_baseline,
+        "clocks": clocks.summary(),
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -108,13 +108,14 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
 
 class GroupedMetadata(tuple):
     """The reference's 5-tuple (ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts)
-    (ops.py:271) plus `num_rows` (the sum of the chunk sizes) as an attribute."""
+    (ops.py:271), plus what the launch needs to know about the matrices behind the table:
+    `num_rows` (sum of the chunk sizes), `dim`, `dtype`, and `keepalive` (contiguous copies
+    made for row-strided inputs, so the addresses in the table stay valid)."""
 
-    num_rows: int
-
-    def __new__(cls, ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts, num_rows):
+    def __new__(cls, ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts,
+                num_rows=None, dim=None, dtype=None, keepalive=None):  # fmt: skip
         self = super().__new__(cls, (ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts))
-        self.num_rows = num_rows
+        self.num_rows, self.dim, self.dtype, self.keepalive = num_rows, dim, dtype, keepalive
         return self
 
 
@@ -124,45 +125,57 @@ def prepare_grouped_metadata(expert_tensors, device):
     Same result as the reference (ops.py:200-271): `ptr_table` int64 [E] of raw
     addresses, `chunk_sizes` int32 [E], `expert_offsets` int64 [E], and the Python
     ints `max_rows` and `num_experts`. The table borrows the addresses: it is valid
-    only while the same tensors stay alive at the same place. All three arrays
-    travel in one host-to-device copy.
+    only while the same tensors stay alive at the same place (row-strided inputs are
+    copied to contiguous rows first, and the copies are kept alive by the result).
+    All three arrays travel in one host-to-device copy.
     """
-    sizes = [int(t.shape[0]) for t in expert_tensors]
-    num_experts = len(sizes)
-    offsets, run = [], 0
-    for s in sizes:
+    num_experts = len(expert_tensors)
+    if num_experts == 0:
+        empty64 = torch.zeros(0, dtype=torch.int64, device=device)
+        return GroupedMetadata(empty64, torch.zeros(0, dtype=torch.int32, device=device), empty64, 0, 0, 0)
+    ref = expert_tensors[0]
+    if ref.dim() != 2:
+        raise ValueError(f"expert tensors must be 2-D [rows, D], got shape {tuple(ref.shape)}")
+    dim, dtype, dev = ref.shape[1], ref.dtype, ref.device
+    ptrs, sizes, offsets, keep, run = [], [], [], None, 0
+    for i, t in enumerate(expert_tensors):
+        if t.dim() != 2 or t.shape[1] != dim or t.dtype != dtype or t.device != dev:
+            raise ValueError(
+                f"expert_tensors[{i}] ({tuple(t.shape)}, {t.dtype}, {t.device}) does not match "
+                f"expert_tensors[0] ([rows, {dim}], {dtype}, {dev})"
+            )
+        if not t.is_contiguous():
+            # the kernels read rows at stride D, as the reference kernel does (ops.py:138)
+            t = t.contiguous()
+            keep = [] if keep is None else keep
+            keep.append(t)
+        n = t.shape[0]
+        ptrs.append(t.data_ptr())
+        sizes.append(n)
         offsets.append(run)
-        run += s
-    ptrs = [t.data_ptr() for t in expert_tensors]
+        run += n
     packed = torch.tensor(ptrs + offsets + sizes, dtype=torch.int64).to(device)
     ptr_table = packed[:num_experts]
     expert_offsets = packed[num_experts : 2 * num_experts]
     chunk_sizes = packed[2 * num_experts :].to(torch.int32)
-    max_rows = max(sizes) if sizes else 0
-    return GroupedMetadata(ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts, run)
+    return GroupedMetadata(ptr_table, chunk_sizes, expert_offsets, max(sizes), num_experts,
+                           run, dim, dtype, keep)  # fmt: skip
 
 
-def _normalise_experts(expert_tensors):
-    """Checks the expert matrices and returns them row-major contiguous."""
-    if len(expert_tensors) == 0:
-        raise ValueError("expert_tensors is empty")
-    ref = expert_tensors[0]
-    if ref.dim() != 2:
-        raise ValueError(f"expert tensors must be 2-D [rows, D], got shape {tuple(ref.shape)}")
-    if ref.dtype not in _DTYPES:
-        raise ValueError(f"unsupported expert dtype {ref.dtype}; use float32, bfloat16 or float16")
-    out = []
-    for i, t in enumerate(expert_tensors):
-        _require_cuda(t, f"expert_tensors[{i}]")
-        if t.dim() != 2 or t.shape[1] != ref.shape[1]:
-            raise ValueError(
-                f"expert_tensors[{i}] has shape {tuple(t.shape)}, expected [rows, {ref.shape[1]}]"
-            )
-        if t.dtype != ref.dtype or t.device != ref.device:
-            raise ValueError(f"expert_tensors[{i}] differs in dtype or device from expert_tensors[0]")
-        # the kernels read rows at stride D, as the reference kernel does (ops.py:138)
-        out.append(t if t.is_contiguous() else t.contiguous())
-    return out
+def _metadata_for(expert_tensors, indices, metadata):
+    """Validated metadata for a launch: built here, or the caller's (trusted, as in the reference)."""
+    if metadata is None:
+        if len(expert_tensors) == 0:
+            raise ValueError("expert_tensors is empty")
+        ref = expert_tensors[0]
+        _require_cuda(ref, "expert_tensors[0]")
+        metadata = prepare_grouped_metadata(expert_tensors, ref.device)
+    elif not isinstance(metadata, GroupedMetadata) or metadata.dim is None:
+        ref = expert_tensors[0]
+        metadata = GroupedMetadata(*metadata, num_rows=int(indices.shape[0]), dim=int(ref.shape[1]), dtype=ref.dtype)
+    if metadata.dtype not in _DTYPES:
+        raise ValueError(f"unsupported expert dtype {metadata.dtype}; use float32, bfloat16 or float16")
+    return metadata
 
 
 def _check_routing(indices, weights, n_rows):
@@ -194,56 +207,68 @@ class CombinePlan:
 
 def build_combine_plan(expert_tensors, indices, weights, n_out, metadata=None) -> CombinePlan:
     """Builds the plan for out[n_out, D]. Four small launches on the current stream."""
-    experts = _normalise_experts(expert_tensors)
-    ref = experts[0]
-    if metadata is None:
-        metadata = prepare_grouped_metadata(experts, ref.device)
+    global launch_count
+    metadata = _metadata_for(expert_tensors, indices, metadata)
     ptr_table, chunk_sizes, expert_offsets, _, num_experts = metadata
-    n_rows = sum(int(t.shape[0]) for t in experts)
+    n_rows, dim, dtype = metadata.num_rows, metadata.dim, metadata.dtype
     indices, weights = _check_routing(indices, weights, n_rows)
-    dim = int(ref.shape[1])
+    device = indices.device
     nbytes = _lib.lib().fmoe_combine_plan_bytes(n_rows, n_out)
-    buf = torch.empty(nbytes, dtype=torch.uint8, device=ref.device)
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
     _lib.call(
         "fmoe_combine_plan",
         ptr_table.data_ptr(), chunk_sizes.data_ptr(), expert_offsets.data_ptr(),
         indices.data_ptr(), _ITYPES[indices.dtype], weights.data_ptr(), _DTYPES[weights.dtype],
-        num_experts, n_rows, n_out, dim, _DTYPES[ref.dtype],
-        buf.data_ptr(), nbytes, _status_word(ref.device).data_ptr(), _stream_ptr(ref.device),
+        num_experts, n_rows, n_out, dim, _DTYPES[dtype],
+        buf.data_ptr(), nbytes, _status_word(device).data_ptr(), _stream_ptr(device),
     )  # fmt: skip
-    return CombinePlan(buf, n_rows, n_out, dim, ref.dtype, (experts, metadata, indices, weights))
+    launch_count += 4
+    return CombinePlan(buf, n_rows, n_out, dim, dtype, (expert_tensors, metadata, indices, weights))
 
 
-def _check_out(out, ref, what="out"):
+def _check_out(out, dim, dtype, what="out"):
     _require_cuda(out, what)
-    if out.dim() != 2 or out.shape[1] != ref.shape[1]:
-        raise ValueError(f"{what} must be [T, {ref.shape[1]}], got {tuple(out.shape)}")
-    if out.dtype != ref.dtype:
-        raise ValueError(f"{what} dtype {out.dtype} differs from the expert dtype {ref.dtype}")
+    if out.dim() != 2 or out.shape[1] != dim:
+        raise ValueError(f"{what} must be [T, {dim}], got {tuple(out.shape)}")
+    if out.dtype != dtype:
+        raise ValueError(f"{what} dtype {out.dtype} differs from the expert dtype {dtype}")
     if out.shape[1] > 1 and out.stride(1) != 1:
         raise ValueError(f"{what} must have unit column stride")
 
 
+# Benchmark hooks: number of kernels this module has launched, and (when set to a
+# list) a pair of CUDA events recorded around every gather launch.
+launch_count = 0
+kernel_events = None
+
+
 def _combine_into(expert_tensors, indices, weights, out, metadata, accumulate, mode=None):
     """Runs the combine into `out` ([T, D], any row stride). Returns the plan (or None)."""
+    global launch_count
     mode = _mode if mode is None else mode
-    experts = _normalise_experts(expert_tensors)
-    ref = experts[0]
-    _check_out(out, ref)
-    n_out, dim = int(out.shape[0]), int(out.shape[1])
+    metadata = _metadata_for(expert_tensors, indices, metadata)
+    dim, dtype = metadata.dim, metadata.dtype
+    _check_out(out, dim, dtype)
+    device = out.device
+    n_out = int(out.shape[0])
     row_stride = int(out.stride(0)) if n_out > 1 else dim
     if mode == "gather":
-        plan = build_combine_plan(experts, indices, weights, n_out, metadata)
+        plan = build_combine_plan(expert_tensors, indices, weights, n_out, metadata)
+        if kernel_events is not None:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         _lib.call(
             "fmoe_combine_gather", plan.buf.data_ptr(), out.data_ptr(), row_stride, plan.n_rows,
-            n_out, dim, _DTYPES[ref.dtype], 1 if accumulate else 0, _stream_ptr(ref.device),
+            n_out, dim, _DTYPES[dtype], 1 if accumulate else 0, _stream_ptr(device),
         )  # fmt: skip
-        _maybe_check(ref.device, "grouped_weighted_scatter_add")
+        if kernel_events is not None:
+            ev1.record()
+            kernel_events.append((ev0, ev1))
+        launch_count += 1
+        _maybe_check(device, "grouped_weighted_scatter_add")
         return plan
-    if metadata is None:
-        metadata = prepare_grouped_metadata(experts, ref.device)
     ptr_table, chunk_sizes, expert_offsets, _, num_experts = metadata
-    n_rows = sum(int(t.shape[0]) for t in experts)
+    n_rows = metadata.num_rows
     indices, weights = _check_routing(indices, weights, n_rows)
     if not accumulate:
         out.zero_()
@@ -251,10 +276,11 @@ def _combine_into(expert_tensors, indices, weights, out, metadata, accumulate, m
         "fmoe_combine_scatter",
         ptr_table.data_ptr(), chunk_sizes.data_ptr(), expert_offsets.data_ptr(),
         indices.data_ptr(), _ITYPES[indices.dtype], weights.data_ptr(), _DTYPES[weights.dtype],
-        out.data_ptr(), row_stride, num_experts, n_rows, n_out, dim, _DTYPES[ref.dtype],
-        _status_word(ref.device).data_ptr(), _stream_ptr(ref.device),
+        out.data_ptr(), row_stride, num_experts, n_rows, n_out, dim, _DTYPES[dtype],
+        _status_word(device).data_ptr(), _stream_ptr(device),
     )  # fmt: skip
-    _maybe_check(ref.device, "grouped_weighted_scatter_add")
+    launch_count += 1
+    _maybe_check(device, "grouped_weighted_scatter_add")
     return None
 
 
@@ -265,17 +291,19 @@ class GroupedWeightedScatterAdd(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, indices, weights, out_shape, *expert_tensors):
-        experts = _normalise_experts(expert_tensors)
-        ref = experts[0]
+        if len(expert_tensors) == 0:
+            raise ValueError("expert_tensors is empty")
+        ref = expert_tensors[0]
+        _require_cuda(ref, "expert_tensors[0]")
         out_shape = tuple(int(s) for s in out_shape)
         if len(out_shape) != 2:
             raise ValueError(f"out_shape must be (T, D), got {out_shape}")
-        # every row is written by the gather kernel, so no zero-fill pass is needed
+        # the gather kernel writes every row itself; only the scatter form needs zeros first
         out = torch.empty(out_shape, device=ref.device, dtype=ref.dtype)
-        plan = _combine_into(experts, indices, weights, out, None, accumulate=False, mode="gather")
-        ctx.plan = plan
+        ctx.plan = _combine_into(expert_tensors, indices, weights, out, None, accumulate=False)
+        ctx.n_out = out_shape[0]
         ctx.save_for_backward(indices, weights, *expert_tensors)
-        ctx.expert_sizes = [int(t.shape[0]) for t in experts]
+        ctx.expert_sizes = [int(t.shape[0]) for t in expert_tensors]
         ctx.weights_dtype = weights.dtype
         ctx.dim = out_shape[1]
         return out
@@ -283,6 +311,9 @@ class GroupedWeightedScatterAdd(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         plan = ctx.plan
+        if plan is None:  # forward ran in scatter mode: the backward still wants the inverse map
+            indices, weights, *experts = ctx.saved_tensors
+            plan = build_combine_plan(experts, indices, weights, ctx.n_out)
         n_rows, dim = plan.n_rows, ctx.dim
         if grad_output.dim() != 2 or (dim > 1 and grad_output.stride(1) != 1):
             grad_output = grad_output.contiguous()
@@ -293,6 +324,8 @@ class GroupedWeightedScatterAdd(torch.autograd.Function):
         want_gw = ctx.needs_input_grad[1]
         grad_w = torch.empty(n_rows, device=device, dtype=torch.float32) if want_gw else None
         row_stride = int(grad_output.stride(0)) if grad_output.shape[0] > 1 else dim
+        global launch_count
+        launch_count += 1
         _lib.call(
             "fmoe_combine_bwd", plan.buf.data_ptr(), grad_output.data_ptr(), row_stride,
             grad_rows.data_ptr(), grad_w.data_ptr() if want_gw else None, n_rows, plan.n_out, dim,

@@ -1,0 +1,56 @@
+"""Host-side logic that needs no GPU: metadata builder against the reference fixture,
+argument checking, the synthetic workloads' routing, and the no-CPU-path rule."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from fastmoe_b200.consts import MoEImplementation
+from fastmoe_b200.kernels import ops
+from fastmoe_b200.workloads import ROUTINGS, sort_routing
+
+
+@pytest.mark.parametrize("name", ["grouped_ragged", "grouped_one_target", "grouped_single"])
+def test_prepare_grouped_metadata_matches_reference(golden, name):
+    g = golden(name)
+    offs = np.concatenate([[0], np.cumsum(g["sizes"])]).astype(int)
+    ex = [torch.from_numpy(g["rows"][offs[e] : offs[e + 1]].copy()) for e in range(len(g["sizes"]))]
+    meta = ops.prepare_grouped_metadata(ex, "cpu")
+    ptr_table, chunk_sizes, expert_offsets, max_rows, num_experts = meta  # unpacks like the reference's tuple
+    assert ptr_table.dtype == torch.int64 and ptr_table.tolist() == [t.data_ptr() for t in ex]
+    assert chunk_sizes.dtype == torch.int32 and np.array_equal(chunk_sizes.numpy(), g["chunk_sizes"])
+    assert expert_offsets.dtype == torch.int64 and np.array_equal(expert_offsets.numpy(), g["expert_offsets"])
+    assert max_rows == int(g["max_rows"]) and num_experts == int(g["num_experts"])
+    assert meta.num_rows == int(g["sizes"].sum()) and meta.dim == g["rows"].shape[1]
+
+
+def test_metadata_keeps_contiguous_copies_alive():
+    wide = torch.randn(6, 16)
+    meta = ops.prepare_grouped_metadata([wide[:, :8], torch.randn(2, 8)], "cpu")
+    assert meta.keepalive is not None and meta[0][0].item() == meta.keepalive[0].data_ptr()
+    with pytest.raises(ValueError):
+        ops.prepare_grouped_metadata([torch.randn(2, 8), torch.randn(2, 4)], "cpu")
+    empty = ops.prepare_grouped_metadata([], "cpu")
+    assert empty[3] == 0 and empty[4] == 0
+
+
+def test_cpu_tensors_are_refused():
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.weighted_scatter_add(torch.zeros(2, 4), torch.zeros(2, dtype=torch.int64), torch.ones(2), (2, 4))
+    with pytest.raises(ValueError):
+        ops.set_combine_mode("triton")
+    assert MoEImplementation.FAST == "fast" and MoEImplementation.STANDARD == "standard"
+    assert ops.HAS_TRITON is False
+
+
+@pytest.mark.parametrize("routing", sorted(ROUTINGS))
+def test_workload_routing_is_valid_and_sorted(routing):
+    T, E, K = 64, 16, 4
+    idx, w = ROUTINGS[routing](T, E, K, seed=1)
+    assert idx.shape == (T, K) and all(len(set(r)) == K for r in idx.tolist())  # K distinct experts
+    assert torch.allclose(w.sum(-1), torch.ones(T), atol=1e-5)
+    rev, sw, counts = sort_routing(idx, w, E)
+    ix = oracle.build_index(idx.numpy(), w.numpy(), E)
+    assert np.array_equal(rev.numpy(), ix["reverse_map"]) and np.array_equal(counts.numpy(), ix["counts"])
+    assert np.array_equal(sw.numpy(), ix["sorted_w"])
