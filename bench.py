@@ -50,6 +50,8 @@ WORKLOADS = {
     # name: (T, D, E, K, routing)
     "combine_cfg2_bf16_T8192_D16384_E256_top8": (8192, 16384, 256, 8, "softmax"),
     "combine_cfg3_zipf_bf16_T8192_D16384_E256_top8": (8192, 16384, 256, 8, "zipf"),
+    # a quarter of the tokens of cfg2, same row width: the size used for ncu captures
+    "combine_ncu_bf16_T2048_D16384_E256_top8": (2048, 16384, 256, 8, "softmax"),
     "combine_small_bf16_T1024_D4096_E64_top8": (1024, 4096, 64, 8, "softmax"),
 }
 DEFAULT_WORKLOAD = "combine_cfg2_bf16_T8192_D16384_E256_top8"

@@ -18,8 +18,11 @@ Differences from the reference that a caller can observe:
 
 from __future__ import annotations
 
+import itertools
+import operator
 import os
 
+import numpy as np
 import torch
 
 from .. import _lib
@@ -37,6 +40,13 @@ __all__ = [
     "read_status",
     "HAS_TRITON",
 ]
+
+_is_contiguous = torch.Tensor.is_contiguous
+_size = torch.Tensor.size
+_data_ptr = torch.Tensor.data_ptr
+_dtype = operator.attrgetter("dtype")
+_get_device = torch.Tensor.get_device
+_head = operator.itemgetter(0)
 
 # The reference exports this flag (ops.py:10,12); this build never uses Triton.
 HAS_TRITON = False
@@ -137,24 +147,33 @@ def prepare_grouped_metadata(expert_tensors, device):
     if ref.dim() != 2:
         raise ValueError(f"expert tensors must be 2-D [rows, D], got shape {tuple(ref.shape)}")
     dim, dtype, dev = ref.shape[1], ref.dtype, ref.device
-    ptrs, sizes, offsets, keep, run = [], [], [], None, 0
-    for i, t in enumerate(expert_tensors):
-        if t.dim() != 2 or t.shape[1] != dim or t.dtype != dtype or t.device != dev:
-            raise ValueError(
-                f"expert_tensors[{i}] ({tuple(t.shape)}, {t.dtype}, {t.device}) does not match "
-                f"expert_tensors[0] ([rows, {dim}], {dtype}, {dev})"
-            )
-        if not t.is_contiguous():
-            # the kernels read rows at stride D, as the reference kernel does (ops.py:138)
-            t = t.contiguous()
-            keep = [] if keep is None else keep
-            keep.append(t)
-        n = t.shape[0]
-        ptrs.append(t.data_ptr())
-        sizes.append(n)
-        offsets.append(run)
-        run += n
-    packed = torch.tensor(ptrs + offsets + sizes, dtype=torch.int64).to(device)
+    keep = None
+    # one C-level pass per property: this runs for every MoE layer call with E tensors
+    if not all(map(_is_contiguous, expert_tensors)):
+        # the kernels read rows at stride D, as the reference kernel does (ops.py:138)
+        expert_tensors = [t if t.is_contiguous() else t.contiguous() for t in expert_tensors]
+        keep = expert_tensors
+    shapes = list(map(_size, expert_tensors))
+    if ({len(sh) == 2 and sh[1] for sh in shapes} != {dim} or set(map(_dtype, expert_tensors)) != {dtype}
+            or set(map(_get_device, expert_tensors)) != {ref.get_device()}):  # fmt: skip
+        for i, t in enumerate(expert_tensors):
+            if t.dim() != 2 or t.shape[1] != dim or t.dtype != dtype or t.device != dev:
+                raise ValueError(
+                    f"expert_tensors[{i}] ({tuple(t.shape)}, {t.dtype}, {t.device}) does not match "
+                    f"expert_tensors[0] ([rows, {dim}], {dtype}, {dev})"
+                )
+    ptrs = list(map(_data_ptr, expert_tensors))
+    sizes = list(map(_head, shapes))
+    offsets = list(itertools.accumulate(sizes, initial=0))
+    run = offsets.pop()
+    device = torch.device(device)
+    if device.type == "cuda":
+        # pinned staging + asynchronous copy: the host never waits for the stream to drain
+        staging = torch.empty(3 * num_experts, dtype=torch.int64, pin_memory=True)
+        staging.numpy()[:] = ptrs + offsets + sizes
+        packed = staging.to(device, non_blocking=True)
+    else:
+        packed = torch.from_numpy(np.array(ptrs + offsets + sizes, dtype=np.int64))
     ptr_table = packed[:num_experts]
     expert_offsets = packed[num_experts : 2 * num_experts]
     chunk_sizes = packed[2 * num_experts :].to(torch.int32)
@@ -303,7 +322,7 @@ class GroupedWeightedScatterAdd(torch.autograd.Function):
         ctx.plan = _combine_into(expert_tensors, indices, weights, out, None, accumulate=False)
         ctx.n_out = out_shape[0]
         ctx.save_for_backward(indices, weights, *expert_tensors)
-        ctx.expert_sizes = [int(t.shape[0]) for t in expert_tensors]
+        ctx.expert_sizes = list(map(_head, map(_size, expert_tensors)))
         ctx.weights_dtype = weights.dtype
         ctx.dim = out_shape[1]
         return out
