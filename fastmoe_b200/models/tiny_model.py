@@ -1,0 +1,244 @@
+"""MoE layer and pipelined block with the module API of polkadot21/fastmoe
+(src/fastmoe/models/tiny_model.py), running the dispatch/combine hot path on the
+sm_100a kernels of this package.
+
+`MoEFeedForward` keeps the reference's constructor, attributes and stage methods
+(gate_and_sort -> dispatch_exchange -> compute_experts -> combine_exchange ->
+unpermute, tiny_model.py:42-420). What differs, on purpose:
+
+  * routing is a fused top-k/softmax kernel plus a stable counting sort instead of
+    torch.topk/softmax/argsort/bincount, and the dispatch permute and the combine
+    are token-major kernels (see fastmoe_b200/kernels);
+  * with more than one rank the received rows are regrouped by expert and gradients
+    flow through the exchange (the reference does neither, see fastmoe_b200/exchange.py);
+  * FAST `forward` hands the per-expert outputs to the grouped combine as separate
+    tensors: no torch.cat of expert results;
+  * `expert_type="swiglu"` gives bias-free SwiGLU experts (gate/up/down) instead of
+    Linear-GELU-Linear.
+
+There is no CPU path: inputs must live on a CUDA device.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.profiler import record_function
+
+from .. import consts, exchange
+from ..kernels import routing
+from ..kernels.ops import grouped_weighted_scatter_add
+
+
+class MultiheadSelfAttention(nn.Module):
+    """Plain full self-attention (the shell around the MoE layer; tiny_model.py:12-28)."""
+
+    def __init__(self, dim, n_heads):
+        super().__init__()
+        if dim % n_heads:
+            raise ValueError("dim must be divisible by n_heads")
+        self.dim, self.n_heads, self.hd = dim, n_heads, dim // n_heads
+        self.qkv = nn.Linear(dim, 3 * dim, bias=False)
+        self.proj = nn.Linear(dim, dim, bias=False)
+
+    def forward(self, x):
+        B, T, D = x.shape
+        q, k, v = self.qkv(x).view(B, T, 3, self.n_heads, self.hd).permute(2, 0, 3, 1, 4)
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=False)
+        return self.proj(y.transpose(1, 2).reshape(B, T, D))
+
+
+class SwiGLUExpert(nn.Module):
+    """down(silu(gate(x)) * up(x)), bias-free."""
+
+    def __init__(self, dim, ff_dim):
+        super().__init__()
+        self.gate = nn.Linear(dim, ff_dim, bias=False)
+        self.up = nn.Linear(dim, ff_dim, bias=False)
+        self.down = nn.Linear(ff_dim, dim, bias=False)
+
+    def forward(self, x):
+        return self.down(F.silu(self.gate(x)) * self.up(x))
+
+
+class MoEFeedForward(nn.Module):
+    def __init__(self, dim, ff_dim, num_experts, top_k, implementation, group=None, expert_type="gelu"):
+        super().__init__()
+        self.dim, self.num_experts, self.top_k = dim, num_experts, top_k
+        self.implementation, self.group = implementation, group
+        if dist.is_initialized():
+            self.world_size, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        else:
+            self.world_size, self.rank = 1, 0
+        if num_experts % self.world_size:
+            raise ValueError(f"num_experts={num_experts} is not divisible by world size {self.world_size}")
+        self.num_local_experts = num_experts // self.world_size
+        self.router = nn.Linear(dim, num_experts, bias=False)
+        if expert_type == "gelu":
+            make = lambda: nn.Sequential(  # noqa: E731
+                nn.Linear(dim, ff_dim, bias=False), nn.GELU(), nn.Linear(ff_dim, dim, bias=False)
+            )
+        elif expert_type == "swiglu":
+            make = lambda: SwiGLUExpert(dim, ff_dim)  # noqa: E731
+        else:
+            raise ValueError(f"expert_type must be 'gelu' or 'swiglu', got {expert_type!r}")
+        self.experts = nn.ModuleList([make() for _ in range(self.num_local_experts)])
+
+    # -- stage 1 ---------------------------------------------------------------------------
+    def gate_and_sort(self, x):
+        """Router, top-k gate, expert-major index and the dispatch permute (tiny_model.py:79-164).
+
+        Returns the reference's 6-tuple: (permuted [N, D], rank_counts int64 [world],
+        expert_counts_by_rank int64 [world, E_local], reverse_map int64 [N],
+        sorted_weights [N], (B, T)).
+        """
+        B, T, D = x.shape
+        x_flat = x.reshape(-1, D)
+        logits = self.router(x_flat)
+        topk_w, topk_idx = routing.route_topk(logits, self.top_k, w_dtype=x.dtype)
+        ix = routing.build_index(topk_idx, topk_w, self.num_experts, self.world_size)
+        permuted = routing.permute_rows(x_flat, ix.slot_of, self.top_k)
+        by_rank = ix.counts.view(self.world_size, self.num_local_experts)
+        return permuted, ix.rank_counts, by_rank, ix.reverse_map, ix.sorted_w, (B, T)
+
+    # -- stage 2 ---------------------------------------------------------------------------
+    def dispatch_exchange(self, permuted_data, send_rank_counts, send_expert_counts):
+        """Sends every routed row to the rank that owns its expert (tiny_model.py:166-218).
+
+        Returns (rows grouped by local expert, recv_splits, send_splits,
+        tokens_per_local_expert). One host synchronisation (the counts).
+        """
+        if self.world_size == 1:
+            counts = send_expert_counts.view(-1).tolist()
+            total = [sum(counts)]
+            return permuted_data, total, list(total), counts
+        _, nested, send_list, recv_list = exchange.exchange_counts(send_expert_counts, send_rank_counts, self.group)
+        recv = exchange.all_to_all_rows(permuted_data, recv_list, send_list, self.group)
+        to_expert_major, to_rank_major, tokens_per_expert = exchange.regroup_indices(nested, recv.device)
+        splits = exchange.SplitList(recv_list)
+        splits.to_expert_major, splits.to_rank_major, splits.counts_by_source = to_expert_major, to_rank_major, nested
+        if self.num_local_experts > 1:
+            recv = recv.index_select(0, to_expert_major)
+        return recv, splits, send_list, tokens_per_expert
+
+    # -- stage 3 ---------------------------------------------------------------------------
+    def expert_outputs(self, recv_data, tokens_per_expert):
+        """One output tensor per local expert, left where each expert wrote it."""
+        outs = []
+        for chunk, expert in zip(recv_data.split(tokens_per_expert, dim=0), self.experts, strict=False):
+            outs.append(expert(chunk) if chunk.shape[0] > 0 else chunk.new_empty(0, self.dim))
+        return outs
+
+    def compute_experts(self, recv_data, tokens_per_expert):
+        """Concatenated expert outputs, rows in the order of recv_data (tiny_model.py:282-294)."""
+        outs = self.expert_outputs(recv_data, tokens_per_expert)
+        return torch.cat(outs, dim=0) if outs else recv_data.new_empty(0, self.dim)
+
+    # -- stage 4 ---------------------------------------------------------------------------
+    def combine_exchange(self, expert_output, recv_splits, send_splits):
+        """Returns expert outputs to the ranks that own the tokens (tiny_model.py:308-339)."""
+        if self.world_size == 1:
+            return expert_output
+        to_rank_major = getattr(recv_splits, "to_rank_major", None)
+        if to_rank_major is not None and self.num_local_experts > 1:
+            expert_output = expert_output.index_select(0, to_rank_major)
+        return exchange.all_to_all_rows(expert_output, list(send_splits), list(recv_splits), self.group)
+
+    # -- stage 5 ---------------------------------------------------------------------------
+    def unpermute(self, x_out, reverse_map_indices, sorted_weights, original_shape):
+        """Weights every routed row by its gate and sums it into its token (tiny_model.py:396-409)."""
+        B, T = original_shape
+        D = self.dim
+        if self.implementation == consts.MoEImplementation.STANDARD:
+            x_out = x_out * sorted_weights.unsqueeze(-1)
+            out = torch.zeros(B * T, D, device=x_out.device, dtype=x_out.dtype)
+            out.index_add_(0, reverse_map_indices, x_out)
+            return out.view(B, T, D)
+        if self.implementation == consts.MoEImplementation.FAST:
+            experts = list(x_out) if isinstance(x_out, (list, tuple)) else [x_out]
+            out = grouped_weighted_scatter_add(experts, reverse_map_indices, sorted_weights, (B * T, D))
+            return out.view(B, T, D)
+        raise NotImplementedError
+
+    def forward(self, x):
+        permuted, send_rank_counts, send_exp_counts, rev_idx, weights, shape = self.gate_and_sort(x)
+        recv, recv_splits, send_splits, tokens_per_expert = self.dispatch_exchange(
+            permuted, send_rank_counts, send_exp_counts
+        )
+        if self.world_size == 1 and self.implementation == consts.MoEImplementation.FAST:
+            # "no-cat": the combine reads the disjoint expert outputs through its pointer table
+            return self.unpermute(self.expert_outputs(recv, tokens_per_expert), rev_idx, weights, shape)
+        expert_out = self.compute_experts(recv, tokens_per_expert)
+        final = self.combine_exchange(expert_out, recv_splits, send_splits)
+        return self.unpermute(final, rev_idx, weights, shape)
+
+
+class PipelinedMoEBlock(nn.Module):
+    """Attention + MoE block that splits the batch into micro-batches and overlaps one
+    micro-batch's token exchange with another's compute on separate CUDA streams
+    (tiny_model.py:466-630 uses two micro-batches on `stream0`/`stream1`; here
+    `num_micro_batches` may be larger and further streams are created on demand).
+    Exchanges are the exact, dynamically sized ones."""
+
+    def __init__(self, dim, n_heads, ff_dim, num_experts, top_k, stream0, stream1,
+                 comm_balance_factor=1, num_micro_batches=2, expert_type="gelu"):  # fmt: skip
+        super().__init__()
+        self.norm1 = nn.LayerNorm(dim)
+        self.attn = MultiheadSelfAttention(dim, n_heads)
+        self.norm2 = nn.LayerNorm(dim)
+        self.moe = MoEFeedForward(dim, ff_dim, num_experts, top_k, consts.MoEImplementation.FAST,
+                                  expert_type=expert_type)  # fmt: skip
+        self.stream0, self.stream1 = stream0, stream1
+        self.comm_balance_factor = comm_balance_factor  # kept for signature parity; padding is never sent
+        self.num_micro_batches = num_micro_batches
+        self._extra_streams = []
+
+    def _streams(self, n):
+        streams = [self.stream0, self.stream1]
+        while len(streams) + len(self._extra_streams) < n:
+            self._extra_streams.append(torch.cuda.Stream())
+        return (streams + self._extra_streams)[:n]
+
+    def forward(self, x):
+        chunks = x.chunk(self.num_micro_batches, dim=0)
+        streams = self._streams(len(chunks))
+        main = torch.cuda.current_stream()
+        state = [dict() for _ in chunks]
+        prev_attn_done = None
+        # phase A: attention + gate + dispatch per micro-batch, staggered so that micro-batch
+        # i+1's attention overlaps micro-batch i's exchange
+        for i, (mb, s) in enumerate(zip(chunks, streams)):
+            s.wait_stream(main)
+            with torch.cuda.stream(s):
+                if prev_attn_done is not None:
+                    s.wait_event(prev_attn_done)
+                with record_function(f"S{i}: Attn {i}"):
+                    resid = mb + self.attn(self.norm1(mb))
+                    gated = self.moe.gate_and_sort(self.norm2(resid))
+                prev_attn_done = torch.cuda.Event()
+                prev_attn_done.record()
+                state[i].update(resid=resid, gated=gated)
+        for i, s in enumerate(streams[: len(chunks)]):
+            with torch.cuda.stream(s):
+                perm, rank_counts, exp_counts, rev, w, shape = state[i]["gated"]
+                with record_function(f"S{i}: Dispatch {i}"):
+                    state[i]["dispatched"] = self.moe.dispatch_exchange(perm, rank_counts, exp_counts)
+        # phase B: experts, return exchange and combine per micro-batch
+        outs = []
+        for i, s in enumerate(streams[: len(chunks)]):
+            with torch.cuda.stream(s):
+                _, _, _, rev, w, shape = state[i]["gated"]
+                recv, recv_splits, send_splits, tokens = state[i]["dispatched"]
+                with record_function(f"S{i}: Experts {i}"):
+                    eo = self.moe.compute_experts(recv, tokens)
+                with record_function(f"S{i}: Combine {i}"):
+                    fd = self.moe.combine_exchange(eo, recv_splits, send_splits)
+                with record_function(f"S{i}: Finalize {i}"):
+                    y = self.moe.unpermute(fd, rev, w, shape) + state[i]["resid"]
+                    y.record_stream(main)  # read by the concatenation on the caller's stream
+                    outs.append(y)
+        for s in streams[: len(chunks)]:
+            main.wait_stream(s)
+        return torch.cat(outs, dim=0)

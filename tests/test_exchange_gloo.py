@@ -1,0 +1,111 @@
+"""Expert-parallel exchange bookkeeping on CPU ranks over gloo (world size 2 and 4):
+counts, uneven all-to-all with gradients, regrouping by expert and the return trip.
+Ground truth is the single-rank computation over all experts."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from fastmoe_b200 import exchange
+from fastmoe_b200.workloads import routing_uniform, sort_routing
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _expert_fn(rows, expert_id):
+    """A stand-in expert with a distinct, non-linear action per expert."""
+    return torch.tanh(rows * (0.5 + 0.1 * expert_id)) * (1.0 + expert_id)
+
+
+def _worker(rank, world, port, E, K, T, D, fail_q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        e_local = E // world
+        torch.manual_seed(100 + rank)
+        x = torch.randn(T, D, dtype=torch.float64, requires_grad=True)
+        idx, w = routing_uniform(T, E, K, seed=100 + rank)
+        rev, sw, counts = sort_routing(idx, w.double(), E)
+        permuted = x[rev]
+        by_rank = counts.view(world, e_local)
+        rank_counts = by_rank.sum(1)
+
+        recv_counts, nested, send_list, recv_list = exchange.exchange_counts(by_rank, rank_counts)
+        assert send_list == rank_counts.tolist() and recv_list == [sum(r) for r in nested]
+        assert recv_counts.tolist() == nested
+        recv = exchange.all_to_all_rows(permuted, recv_list, send_list)
+        to_em, to_rm, tokens = exchange.regroup_indices(nested, recv.device)
+        assert tokens == [sum(nested[s][e] for s in range(world)) for e in range(e_local)]
+        assert torch.equal(to_em[to_rm], torch.arange(recv.shape[0]))
+        grouped = recv.index_select(0, to_em)
+        outs = [
+            _expert_fn(chunk, rank * e_local + e) for e, chunk in enumerate(grouped.split(tokens))
+        ]
+        back = exchange.all_to_all_rows(torch.cat(outs).index_select(0, to_rm), send_list, recv_list)
+        out = torch.zeros(T, D, dtype=torch.float64).index_add(0, rev, back * sw[:, None])
+        coeff = torch.randn(T, D, dtype=torch.float64)
+        (out * coeff).sum().backward()
+
+        # single-rank ground truth over all experts
+        x2 = x.detach().clone().requires_grad_(True)
+        p2 = x2[rev]
+        o2 = torch.cat([_expert_fn(c, e) for e, c in enumerate(p2.split(counts.tolist()))])
+        out2 = torch.zeros(T, D, dtype=torch.float64).index_add(0, rev, o2 * sw[:, None])
+        (out2 * coeff).sum().backward()
+        assert torch.allclose(out, out2, rtol=1e-12, atol=1e-12)
+        assert torch.allclose(x.grad, x2.grad, rtol=1e-12, atol=1e-12)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:  # surface the failure in the parent
+        import traceback
+
+        fail_q.put(f"rank {rank}: {exc}\n{traceback.format_exc()}")
+        raise
+
+
+@pytest.mark.parametrize("world,E", [(2, 2), (2, 8), (4, 8)])
+def test_exchange_matches_single_rank(world, E):
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    procs = [ctx.Process(target=_worker, args=(r, world, _free_port_cached(world, E), E, 3 if E > 2 else 2, 24, 5, q))
+             for r in range(world)]  # fmt: skip
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    msgs = []
+    while not q.empty():
+        msgs.append(q.get())
+    assert not msgs, "\n".join(msgs)
+    assert all(p.exitcode == 0 for p in procs)
+
+
+_ports = {}
+
+
+def _free_port_cached(world, E):
+    key = (world, E)
+    if key not in _ports:
+        _ports[key] = _free_port()
+    return _ports[key]
+
+
+def test_regroup_indices_small():
+    # 2 source ranks, 3 local experts; arrival order is (source, expert)
+    nested = [[2, 0, 1], [1, 2, 0]]
+    to_em, to_rm, tokens = exchange.regroup_indices(nested, "cpu")
+    assert tokens == [3, 2, 1]
+    # rank-major rows: s0e0 s0e0 s0e2 | s1e0 s1e1 s1e1 -> expert-major: e0(s0,s0,s1) e1(s1,s1) e2(s0)
+    assert to_em.tolist() == [0, 1, 3, 4, 5, 2]
+    assert np.array_equal(to_rm.numpy(), np.argsort(to_em.numpy()))
+    empty = exchange.regroup_indices([[0, 0], [0, 0]], "cpu")
+    assert empty[0].numel() == 0 and empty[2] == [0, 0]

@@ -1,0 +1,142 @@
+"""The MoE layer module on the GPU against the reference's CPU layer (fixture) and the oracle:
+config 1 (fp32 layer forward+backward), the dispatch+combine pair under autograd (config 4's
+path), and the size-independent identity property at config 4's full size."""
+
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from fastmoe_b200.consts import MoEImplementation
+from fastmoe_b200.kernels import ops, routing
+from fastmoe_b200.models.tiny_model import MoEFeedForward
+from fastmoe_b200.workloads import routing_uniform
+from util import assert_close, to_np
+
+sys.path.insert(0, str(Path(__file__).parent / "golden"))
+from make_inputs import layer_cfg1_weights  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _cfg1_layer(impl):
+    router, w1, w2, x, target = layer_cfg1_weights()
+    moe = MoEFeedForward(128, 512, 8, 2, impl).to(DEV)
+    with torch.no_grad():
+        moe.router.weight.copy_(torch.from_numpy(router))
+        for e in range(8):
+            moe.experts[e][0].weight.copy_(torch.from_numpy(w1[e]))
+            moe.experts[e][2].weight.copy_(torch.from_numpy(w2[e]))
+    xt = torch.from_numpy(x).to(DEV).view(1, 256, 128).requires_grad_(True)
+    return moe, xt, torch.from_numpy(target).to(DEV).view(1, 256, 128)
+
+
+@pytest.mark.parametrize("impl", [MoEImplementation.FAST, MoEImplementation.STANDARD])
+def test_config1_layer_forward_backward(golden, impl):
+    """T=256, D=128, E=8, top-2, fp32, weights N(0, 0.02): forward and backward of the whole layer
+    against what the reference's CPU layer produced. 1e-4 of the largest magnitude: the two
+    GEMMs per expert run on cuBLAS with another summation order than the CPU's."""
+    g = golden("layer_cfg1")
+    moe, x, target = _cfg1_layer(impl)
+    out = moe(x)
+    loss = ((out - target) ** 2).sum()
+    loss.backward()
+    tol = 1e-4
+
+    def rel(a, b):
+        return float(np.abs(to_np(a) - b).max()) / float(np.abs(b).max())
+
+    assert rel(out[0], g["out"]) <= tol
+    assert rel(x.grad[0], g["x_grad"]) <= tol
+    assert rel(moe.router.weight.grad, g["router_grad"]) <= tol
+    assert rel(moe.experts[0][0].weight.grad, g["w1_grad_e0"]) <= tol
+    assert rel(moe.experts[7][2].weight.grad, g["w2_grad_e7"]) <= tol
+    assert abs(float(loss.detach()) - float(g["loss"])) <= tol * float(g["loss"])
+    assert ops.read_status() == 0
+
+
+def test_gate_and_sort_contract():
+    moe, x, _ = _cfg1_layer(MoEImplementation.FAST)
+    permuted, rank_counts, by_rank, rev, w, shape = moe.gate_and_sort(x)
+    assert shape == (1, 256) and permuted.shape == (512, 128)
+    assert rank_counts.dtype == torch.int64 and rank_counts.tolist() == [512]
+    assert by_rank.dtype == torch.int64 and by_rank.shape == (1, 8) and int(by_rank.sum()) == 512
+    assert rev.dtype == torch.int64 and w.dtype == x.dtype
+    logits = to_np(moe.router(x.view(-1, 128)))
+    o_idx, o_w = oracle.topk_softmax(logits, 2)
+    ix = oracle.build_index(o_idx, o_w, 8)
+    assert np.array_equal(rev.cpu().numpy(), ix["reverse_map"])
+    assert np.array_equal(by_rank.cpu().numpy().reshape(-1), ix["counts"])
+    np.testing.assert_allclose(to_np(w), ix["sorted_w"], rtol=2e-6, atol=1e-7)
+    assert np.array_equal(to_np(permuted), to_np(x.view(-1, 128))[ix["reverse_map"]])
+    recv, recv_splits, send_splits, tokens = moe.dispatch_exchange(permuted, rank_counts, by_rank)
+    assert recv is permuted and recv_splits == [512] and send_splits == [512] and tokens == ix["counts"].tolist()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dispatch_combine_autograd_against_oracle(dtype):
+    """Config 4's path at a size the oracle handles in a blink: uniform top-8 routing over 256
+    experts, permute -> per-expert scale (stands in for the FFN) -> combine; checks permuted,
+    out, dx and d(gate)."""
+    T, D, E, K = 512, 7168, 256, 8
+    idx, w = routing_uniform(T, E, K, seed=4)
+    rng = np.random.default_rng(4)
+    x = torch.from_numpy(rng.standard_normal((T, D)).astype(np.float32)).to(DEV).to(dtype).requires_grad_(True)
+    gate = w.to(DEV).to(dtype).requires_grad_(True)
+    grad_out = torch.from_numpy(rng.standard_normal((T, D)).astype(np.float32)).to(DEV).to(dtype)
+    scale = torch.linspace(0.5, 1.5, E, device=DEV)
+
+    ix = routing.build_index(idx.to(DEV), gate, E)
+    permuted = routing.permute_rows(x, ix.slot_of, K)
+    counts = ix.counts.tolist()
+    outs = [c * scale[e].to(dtype) for e, c in enumerate(permuted.split(counts))]
+    out = ops.grouped_weighted_scatter_add(outs, ix.reverse_map, ix.sorted_w, (T, D))
+    out.backward(grad_out)
+
+    o = oracle.build_index(idx.numpy(), to_np(gate), E)
+    assert np.array_equal(ix.reverse_map.cpu().numpy(), o["reverse_map"])
+    assert np.array_equal(ix.counts.cpu().numpy(), o["counts"]) and np.array_equal(ix.offsets.cpu().numpy(), o["offsets"])
+    rm = o["reverse_map"]
+    perm_ref = oracle.permute(to_np(x), rm)
+    assert np.array_equal(to_np(permuted), perm_ref)
+    rows_ref = np.concatenate([to_np(t) for t in outs], 0)  # the kernels' actual inputs
+    out_ref = oracle.combine([rows_ref], rm, o["sorted_w"], T)
+    assert_close(out, out_ref, dtype, "out")
+    g_rows, g_w = oracle.combine_bwd(rows_ref, rm, o["sorted_w"], to_np(grad_out))
+    s_of_row = np.repeat(to_np(scale), o["counts"])
+    if dtype == torch.bfloat16:  # the scale multiply's backward rounds to bf16 once more
+        g_rows = to_np(torch.from_numpy(g_rows).to(dtype)) * np.repeat(to_np(scale.to(dtype)), o["counts"])[:, None]
+    else:
+        g_rows = g_rows * s_of_row[:, None]
+    dx_ref = oracle.permute_bwd(g_rows, rm, T)
+    assert_close(x.grad, dx_ref, dtype, "dx")
+    dgate_ref = np.empty(T * K, np.float32)
+    dgate_ref[:] = g_w[o["slot_of"]]
+    assert_close(gate.grad.reshape(-1), dgate_ref, dtype, "d(gate)")
+
+
+def test_config4_full_size_identity_property():
+    """T=16384, D=7168, E=256, top-8, bf16. With identity experts and gate weights that sum to one,
+    combine(permute(x)) must return x, and the backward must return the upstream gradient."""
+    T, D, E, K = 16384, 7168, 256, 8
+    idx, w = routing_uniform(T, E, K, seed=9)
+    gen = torch.Generator(device=DEV).manual_seed(9)
+    x = torch.randn(T, D, generator=gen, device=DEV, dtype=torch.bfloat16).requires_grad_(True)
+    grad_out = torch.randn(T, D, generator=gen, device=DEV, dtype=torch.bfloat16)
+    gate = w.to(DEV)  # fp32 weights: they sum to 1 to fp32 accuracy
+    ix = routing.build_index(idx.to(DEV), gate, E)
+    assert int(ix.counts.sum()) == T * K and bool((ix.counts == torch.bincount(idx.reshape(-1), minlength=E).to(DEV)).all())
+    permuted = routing.permute_rows(x, ix.slot_of, K)
+    assert torch.equal(permuted, x.detach()[ix.reverse_map])
+    outs = list(permuted.split(ix.counts.tolist()))
+    out = ops.grouped_weighted_scatter_add(outs, ix.reverse_map, ix.sorted_w, (T, D))
+    out.backward(grad_out)
+    err = float((out.float() - x.detach().float()).abs().max() / x.detach().float().abs().max())
+    assert err <= 2e-2, err
+    gerr = float((x.grad.float() - grad_out.float()).abs().max() / grad_out.float().abs().max())
+    assert gerr <= 2e-2, gerr
+    assert ops.read_status() == 0
