@@ -129,6 +129,33 @@ int fmoe_combine_gather(const void* plan, void* out, int64_t out_row_stride, int
                         int64_t T, int64_t D, int dtype, int accumulate, void* stream);
 
 /*
+ * The planned combine (plan + gather in one call) for callers that can neither pass
+ * scratch memory nor let the library allocate: plugin hosts whose own pool has
+ * claimed all device memory, or serving loops that cannot afford the device-wide
+ * stall of a cudaMalloc. No counterpart in the reference (it allocates through
+ * torch on every call); arguments as for fmoe_combine_plan and fmoe_combine_gather.
+ *
+ * The plan is built in an array of FMOE_STATIC_SCRATCH_BYTES (4 MiB) that is part of
+ * the library's device image: every GPU that loads the library holds it until the
+ * process exits. Problems whose plan is larger (fmoe_combine_plan_bytes(N, T) >
+ * FMOE_STATIC_SCRATCH_BYTES; N=131072 rows into T=16384 outputs still fits) are
+ * refused with FMOE_ERR_WORKSPACE. The call allocates and frees nothing.
+ *
+ * The first call on each device looks up the array's device address (that device
+ * must be current, as for every call): make that first call before any stream
+ * capture begins. All calls share the one array per device and it keeps the last
+ * call's contents (what must start at zero is cleared on `stream` each time), so two
+ * calls that may overlap on the GPU, e.g. on different streams without an ordering
+ * between them, race on it; order them yourself.
+ */
+#define FMOE_STATIC_SCRATCH_BYTES 4194304
+int fmoe_combine_fwd_static(const int64_t* ptr_table, const int32_t* chunk_sizes,
+                            const int64_t* expert_offsets, const void* idx, int idx_type,
+                            const void* w, int w_dtype, void* out, int64_t out_row_stride,
+                            int64_t E, int64_t N, int64_t T, int64_t D, int dtype,
+                            int accumulate, int32_t* status, void* stream);
+
+/*
  * Backward of the combine (replaces `GroupedWeightedScatterAdd.backward`,
  * ops.py:334-359, and adds the gate gradient the reference leaves out at
  * ops.py:358-359; the reference's CPU path produces it through autograd):
