@@ -55,10 +55,13 @@ WORKLOADS = {
     "combine_small_bf16_T1024_D4096_E64_top8": (1024, 4096, 64, 8, "softmax"),
 }
 DEFAULT_WORKLOAD = "combine_cfg2_bf16_T8192_D16384_E256_top8"
+# dispatch permute + combine, forward and backward under autograd: (T, D, E, K)
+CFG4 = {"dispatch_combine_cfg4_bf16_T16384_D7168_E256_top8": (16384, 7168, 256, 8)}
 
-# DRAM bytes (read + write) of one gather launch on the default workload, from the
-# ncu capture summarised in profiles/combine_gather_cfg2.md; None until captured.
-NCU_TRAFFIC_BYTES = {DEFAULT_WORKLOAD: None}
+# DRAM bytes (read + write) of one gather launch on the default workload: the ncu
+# capture of the quarter-size case (profiles/combine_gather_cfg2.md) scaled by its
+# 4x tokens; traffic grows in proportion to tokens.
+NCU_TRAFFIC_BYTES = {DEFAULT_WORKLOAD: 4 * (537_091_584 + 45_902_592)}
 
 FALLBACK_HBM_GBS = 6650.0
 
@@ -238,7 +241,7 @@ def run_ours(args, rank, world, local_rank):
         out = step()
     barrier()
 
-    ops.kernel_events = []  # (start, end) CUDA events around every gather launch
+    ops.kernel_events = {}  # entry point -> (start, end) CUDA events around every call
     launches0 = ops.launch_count
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
@@ -249,7 +252,8 @@ def run_ours(args, rank, world, local_rank):
         end.record()
         barrier()
     elapsed_ms = start.elapsed_time(end)
-    gather_ms = [s.elapsed_time(e) for s, e in ops.kernel_events]
+    gather_ms = [s.elapsed_time(e) for s, e in ops.kernel_events.get("fmoe_combine_gather", [])]
+    plan_ms = [s.elapsed_time(e) for s, e in ops.kernel_events.get("fmoe_combine_plan", [])]
     launches = ops.launch_count - launches0
     ops.kernel_events = None
     assert ops.read_status(device) == 0, "kernels flagged skipped rows"
@@ -313,6 +317,7 @@ def run_ours(args, rank, world, local_rank):
         "kernel_ms": kernel_ms,
         "algorithmic_bytes": nbytes,
         "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+        "plan_build_ms": statistics.mean(plan_ms) if plan_ms else None,
     }
 
     # CPU baseline: the oracle port on this box's cores, whole workload, a few passes
@@ -357,13 +362,99 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_cfg4(args, rank, world, local_rank):
+    """Index build + dispatch permute + combine, forward and backward, identity experts.
+    Reports whole-chain GB/s of algorithmic bytes and a roofline entry per kernel."""
+    import torch
+    import torch.distributed as dist
+
+    from fastmoe_b200.kernels import ops, routing
+    from fastmoe_b200.workloads import routing_uniform
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    T, D, E, K = CFG4[args.workload]
+    N, s = T * K, 2
+    idx, w = routing_uniform(T, E, K, seed=rank)
+    idx, gate = idx.to(dev), w.to(dev).bfloat16().requires_grad_(True)
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    x = torch.randn(T, D, generator=gen, device=dev, dtype=torch.bfloat16).requires_grad_(True)
+    grad_out = torch.randn(T, D, generator=gen, device=dev, dtype=torch.bfloat16)
+    # per-kernel algorithmic bytes (payload only; index bytes are < 0.1%)
+    alg = {
+        "fmoe_permute_fwd": T * D * s + N * D * s,
+        "fmoe_combine_gather": N * D * s + T * D * s,
+        "fmoe_combine_bwd": T * D * s + 2 * N * D * s,
+        "fmoe_permute_bwd": N * D * s + T * D * s,
+    }
+    total_bytes = sum(alg.values())
+
+    def step():
+        x.grad = gate.grad = None
+        ix = routing.build_index(idx, gate, E)
+        permuted = routing.permute_rows(x, ix.slot_of, K)
+        out = ops.grouped_weighted_scatter_add([permuted], ix.reverse_map, ix.sorted_w, (T, D))
+        out.backward(grad_out)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    ops.kernel_events = {}
+    launches0 = ops.launch_count
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            step()
+        end.record()
+        barrier()
+    elapsed_ms = start.elapsed_time(end)
+    events, ops.kernel_events = ops.kernel_events, None
+    launches = ops.launch_count - launches0
+    stats = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(stats[0])
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak()
+    kernels = {}
+    for name, pairs in events.items():
+        ms = statistics.mean(a.elapsed_time(b) for a, b in pairs)
+        entry = {"ms": ms, "calls": len(pairs)}
+        if name in alg:
+            entry.update(algorithmic_bytes=alg[name], achieved=alg[name] / ms / 1e6, frac=alg[name] / ms / 1e6 / peak)
+        kernels[name] = entry
+    top = max(alg, key=lambda k: kernels[k]["ms"])
+    line = {
+        "metric": "dispatch_combine_hbm_gbs", "value": total_bytes * world * args.steps / (elapsed_ms / 1e3) / 1e9,
+        "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "T": T, "D": D, "E": E, "top_k": K, "routing": "uniform",
+                   "l2": "inputs (1.9 GB of routed rows) exceed the 126 MB L2", "multi_gpu": "replicas only"},
+        "e2e": None, "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": top, "achieved": kernels[top]["achieved"], "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": kernels[top]["frac"], "traffic": None},
+        "kernels": kernels, "clocks": clocks.summary(),
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(CFG4), default=DEFAULT_WORKLOAD)
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -381,7 +472,10 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.workload in CFG4:
+            run_cfg4(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -209,6 +209,14 @@ __device__ __forceinline__ uint4 ld_keep16(const uint4* p) {
                : "l"(p));
   return v;
 }
+// Rows that several warps of one CTA read at about the same time: let L1 keep them.
+__device__ __forceinline__ uint4 ld_cached16(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
 __device__ __forceinline__ void st_stream16(uint4* p, const uint4& v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)

@@ -106,34 +106,46 @@ __global__ void __launch_bounds__(256)
   if (flags && status != nullptr) atomicOr(status, flags);
 }
 
-// Single CTA: per expert, exclusive prefix over the chunks (in place) and the
-// total; then the exclusive prefix over experts and the per-rank sums.
+// Single CTA of 32 warps. Phase 1: each warp takes experts warp, warp+32, ... and
+// turns that expert's per-chunk counts into an exclusive prefix over the chunks (in
+// place), 32 chunks per step with a shuffle scan. Phase 2: exclusive prefix over the
+// experts' totals (offsets) and the per-rank sums.
 __global__ void __launch_bounds__(1024)
     index_scan_kernel(int32_t* __restrict__ chunk_hist, int64_t nchunks, int E, int world,
                       int64_t* __restrict__ counts, int64_t* __restrict__ offsets,
                       int64_t* __restrict__ rank_counts) {
+  extern __shared__ int32_t totals[];  // [E]
   __shared__ int64_t warp_sums[32];
   __shared__ int64_t carry_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   if (threadIdx.x == 0) carry_s = 0;
   if (threadIdx.x < 32) warp_sums[threadIdx.x] = 0;
   for (int r = threadIdx.x; r < world; r += blockDim.x) rank_counts[r] = 0;
+
+  for (int e = warp; e < E; e += nwarps) {
+    int32_t carry = 0;
+#pragma unroll 4
+    for (int64_t base = 0; base < nchunks; base += 32) {
+      const int64_t c = base + lane;
+      const int32_t v = c < nchunks ? chunk_hist[c * E + e] : 0;
+      int32_t incl = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int32_t n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+      }
+      if (c < nchunks) chunk_hist[c * E + e] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) totals[e] = carry;
+  }
   __syncthreads();
+
   const int e_local = E / world;
   for (int base = 0; base < E; base += blockDim.x) {
     const int e = base + threadIdx.x;
-    int64_t total = 0;
-    if (e < E) {
-      int32_t run = 0;
-      for (int64_t c = 0; c < nchunks; ++c) {
-        const int32_t v = chunk_hist[c * E + e];
-        chunk_hist[c * E + e] = run;
-        run += v;
-      }
-      total = run;
-      counts[e] = total;
-    }
-    // block-wide exclusive scan of `total`
+    const int64_t total = e < E ? totals[e] : 0;
+    if (e < E) counts[e] = total;
     int64_t incl = total;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -143,13 +155,13 @@ __global__ void __launch_bounds__(1024)
     if (lane == 31) warp_sums[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-      int64_t s = lane < nwarps ? warp_sums[lane] : 0;
+      int64_t sum = lane < nwarps ? warp_sums[lane] : 0;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
-        const int64_t n = __shfl_up_sync(0xffffffffu, s, d);
-        if (lane >= d) s += n;
+        const int64_t n = __shfl_up_sync(0xffffffffu, sum, d);
+        if (lane >= d) sum += n;
       }
-      warp_sums[lane] = s;
+      warp_sums[lane] = sum;
     }
     __syncthreads();
     const int64_t carry = carry_s;
@@ -289,8 +301,7 @@ extern "C" int fmoe_build_index(const int64_t* topk_idx, const void* topk_w, int
                                                      static_cast<int>(K), chunk_hist, status);
     FMOE_CUDA(cudaGetLastError());
   }
-  const int scan_threads = E >= 1024 ? 1024 : static_cast<int>((E + 31) / 32 * 32);
-  index_scan_kernel<<<1, scan_threads, 0, s>>>(chunk_hist, nchunks, static_cast<int>(E),
+  index_scan_kernel<<<1, 1024, sizeof(int32_t) * static_cast<size_t>(E), s>>>(chunk_hist, nchunks, static_cast<int>(E),
                                                static_cast<int>(world), counts, offsets, rank_counts);
   FMOE_CUDA(cudaGetLastError());
   if (nchunks > 0) {

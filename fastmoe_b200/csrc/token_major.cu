@@ -18,8 +18,8 @@ namespace fmoe {
 // ---- tuning knobs (fmoe_tune) -------------------------------------------------
 static int g_gather_v = 0;         // vectors per thread, 0 = choose from D
 static int g_gather_threads = 0;   // threads per CTA, 0 = choose from D
-static int g_gather_ctas_per_sm = 0;  // persistent grid = 148 * this; 0 = one CTA per item
-static int g_bwd_ctas_per_sm = 4;
+static int g_gather_ctas_per_sm = -1;  // persistent grid = 148 * this; 0 = one CTA per item; -1 = auto
+static int g_bwd_ctas_per_sm = 3;
 
 struct TileCfg {
   int threads;
@@ -47,6 +47,16 @@ static TileCfg pick_tile(int64_t dvec, int pref_v, int force_threads, int max_v 
     }
   }
   return best;
+}
+
+// Grid for `items` work items: one CTA per item, or a persistent grid of
+// 148 x ctas_per_sm CTAs that stride over the items.
+static int64_t clamp_grid(int64_t items, int ctas_per_sm) {
+  int64_t grid = items;
+  if (ctas_per_sm > 0 && items > static_cast<int64_t>(kNumSMs) * ctas_per_sm)
+    grid = static_cast<int64_t>(kNumSMs) * ctas_per_sm;
+  if (grid > 0x7fffffffll) grid = 0x7fffffffll;
+  return grid;
 }
 
 // ---- row sources ----------------------------------------------------------------
@@ -216,125 +226,91 @@ static int launch_gather_sum(const Source& src, void* out, int64_t out_row_strid
   }
   const int64_t dvec = D / El::kVec;
   const TileCfg cfg = pick_tile(dvec, g_gather_v > 0 ? g_gather_v : 2, g_gather_threads);
-  const int64_t items = T * cfg.tiles;
-  int64_t grid = items;
-  if (g_gather_ctas_per_sm > 0 && items > static_cast<int64_t>(kNumSMs) * g_gather_ctas_per_sm)
-    grid = static_cast<int64_t>(kNumSMs) * g_gather_ctas_per_sm;
-  if (grid > 0x7fffffffll) grid = 0x7fffffffll;
-  const int g = static_cast<int>(grid);
+  auto launch = [&](auto kernel) {
+    int ctas = g_gather_ctas_per_sm;
+    if (ctas < 0) {  // auto: exactly as many CTAs as stay resident
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, kernel, cfg.threads, 0) != cudaSuccess ||
+          ctas < 1)
+        ctas = 1;
+    }
+    const int g = static_cast<int>(clamp_grid(T * cfg.tiles, ctas));
+    kernel<<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);
+  };
   switch (cfg.v) {
-    case 1:
-      gather_sum_kernel<DT, 1, WEIGHTED, Source><<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);
-      break;
-    case 2:
-      gather_sum_kernel<DT, 2, WEIGHTED, Source><<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);
-      break;
-    default:
-      gather_sum_kernel<DT, 4, WEIGHTED, Source><<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);
-      break;
+    case 1: launch(gather_sum_kernel<DT, 1, WEIGHTED, Source>); break;
+    case 2: launch(gather_sum_kernel<DT, 2, WEIGHTED, Source>); break;
+    default: launch(gather_sum_kernel<DT, 4, WEIGHTED, Source>); break;
   }
   return check_launch("gather_sum_kernel");
 }
 
 // ---- combine backward ---------------------------------------------------------------
-// One CTA per output row: grad_out[t] is read once per chunk of 8 routed rows,
-// each routed row gets its scaled copy, and the gate gradient is the row dot
-// with the forward source row, reduced across the CTA in a fixed order.
-constexpr int kBwdRows = 8;
+// One warp per routed row: it streams grad_out[t] (shared through L1/L2 with the
+// other warps working on the same token) and, for the gate gradient, the forward
+// source row; writes the scaled copy; and reduces the row dot with shuffles in a
+// fixed order. Warps never wait for each other. A CTA takes `group` consecutive
+// tokens per step so that its 8 warps stay busy when tokens have fewer than 8 rows.
+constexpr int kBwdWarps = 8;
 
-template <int DT, int V, bool WITH_GW>
-__global__ void __launch_bounds__(256)
+template <int DT, bool WITH_GW>
+__global__ void __launch_bounds__(kBwdWarps * 32)
     combine_bwd_kernel(const int32_t* __restrict__ seg_off, const int32_t* __restrict__ row_of_slot,
                        const int64_t* __restrict__ src_sorted, const float* __restrict__ w_sorted,
                        const void* __restrict__ grad_out, int64_t go_row_stride,
                        void* __restrict__ grad_rows, float* __restrict__ grad_w, int64_t T,
-                       int64_t D, int64_t dvec, int tiles) {
+                       int64_t D, int64_t dvec, int group) {
   using El = Elem<DT>;
   using Ty = typename El::type;
-  __shared__ float red[8][kBwdRows];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  constexpr int U = 4;  // vectors in flight per lane and stream
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t items = (T + group - 1) / group;
 
-  for (int64_t t = blockIdx.x; t < T; t += gridDim.x) {
-    const int beg = seg_off[t], end = seg_off[t + 1];
-    const uint4* gorow = reinterpret_cast<const uint4*>(reinterpret_cast<const Ty*>(grad_out) + t * go_row_stride);
-    for (int jc = beg; jc < end; jc += kBwdRows) {
-      const int nj = min(kBwdRows, end - jc);
-      int64_t g[kBwdRows];
-      float w[kBwdRows];
-      const char* p[kBwdRows];
-      float dot[kBwdRows];
+  for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
+    const int64_t t0 = item * group;
+    const int64_t t1 = min(T, t0 + group);
+    const int beg = seg_off[t0], end = seg_off[t1];
+    int64_t t = t0;
+    for (int j = beg + warp; j < end; j += kBwdWarps) {
+      while (t + 1 < t1 && seg_off[t + 1] <= j) ++t;  // token that owns slot j
+      const int64_t g = row_of_slot[j];
+      const float w = w_sorted[j];
+      const char* p = reinterpret_cast<const char*>(src_sorted[j]);
+      const uint4* gorow =
+          reinterpret_cast<const uint4*>(reinterpret_cast<const Ty*>(grad_out) + t * go_row_stride);
+      uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<Ty*>(grad_rows) + g * D);
+      float dot = 0.f;
+      for (int64_t c0 = lane; c0 < dvec; c0 += 32 * U) {
+        uint4 gv[U], xv[U];
 #pragma unroll
-      for (int u = 0; u < kBwdRows; ++u) {
-        dot[u] = 0.f;
-        g[u] = -1;
-        w[u] = 0.f;
-        p[u] = nullptr;
-        if (u < nj) {
-          g[u] = row_of_slot[jc + u];
-          w[u] = w_sorted[jc + u];
-          p[u] = reinterpret_cast<const char*>(src_sorted[jc + u]);
-        }
-      }
-      for (int tile = 0; tile < tiles; ++tile) {
-        int64_t col[V];
-        float go[V][El::kVec];
-#pragma unroll
-        for (int v = 0; v < V; ++v) {
-          col[v] = (static_cast<int64_t>(tile) * V + v) * blockDim.x + threadIdx.x;
-          if (col[v] < dvec) {
-            unpack16<DT>(ld_keep16(gorow + col[v]), go[v]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < El::kVec; ++i) go[v][i] = 0.f;
+        for (int u = 0; u < U; ++u) {
+          const int64_t c = c0 + 32 * u;
+          if (c < dvec) {
+            gv[u] = ld_cached16(gorow + c);
+            if (WITH_GW) xv[u] = p != nullptr ? load_row_vec<DT>(p, c) : make_uint4(0, 0, 0, 0);
           }
         }
-        uint4 x[kBwdRows][V];
-        if (WITH_GW) {
 #pragma unroll
-          for (int u = 0; u < kBwdRows; ++u)
+        for (int u = 0; u < U; ++u) {
+          const int64_t c = c0 + 32 * u;
+          if (c < dvec) {
+            float go[El::kVec], f[El::kVec];
+            unpack16<DT>(gv[u], go);
 #pragma unroll
-            for (int v = 0; v < V; ++v)
-              x[u][v] = (p[u] != nullptr && col[v] < dvec) ? load_row_vec<DT>(p[u], col[v])
-                                                           : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int u = 0; u < kBwdRows; ++u) {
-          if (g[u] < 0) continue;
-          uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<Ty*>(grad_rows) + g[u] * D);
-#pragma unroll
-          for (int v = 0; v < V; ++v) {
-            if (col[v] >= dvec) continue;
-            float f[El::kVec];
-#pragma unroll
-            for (int i = 0; i < El::kVec; ++i) f[i] = __fmul_rn(go[v][i], w[u]);
-            st_stream16(drow + col[v], pack16<DT>(f));
+            for (int i = 0; i < El::kVec; ++i) f[i] = __fmul_rn(go[i], w);
+            st_stream16(drow + c, pack16<DT>(f));
             if (WITH_GW) {
               float xf[El::kVec];
-              unpack16<DT>(x[u][v], xf);
+              unpack16<DT>(xv[u], xf);
 #pragma unroll
-              for (int i = 0; i < El::kVec; ++i) dot[u] = fmaf(go[v][i], xf[i], dot[u]);
+              for (int i = 0; i < El::kVec; ++i) dot = fmaf(go[i], xf[i], dot);
             }
           }
         }
       }
       if (WITH_GW) {
 #pragma unroll
-        for (int u = 0; u < kBwdRows; ++u) {
-          float d = dot[u];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-          if (lane == 0) red[warp][u] = d;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int u = 0; u < kBwdRows; ++u) {
-          if (threadIdx.x == u && u < nj) {  // g[] is uniform across the CTA
-            float d = 0.f;
-            for (int wv = 0; wv < nwarps; ++wv) d += red[wv][u];
-            grad_w[g[u]] = d;
-          }
-        }
-        __syncthreads();
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0) grad_w[g] = dot;
       }
     }
   }
@@ -361,13 +337,19 @@ __global__ void __launch_bounds__(256)
       col[v] = (static_cast<int64_t>(tile) * V + v) * blockDim.x + threadIdx.x;
       if (col[v] < dvec) val[v] = ld_stream16(xrow + col[v]);
     }
-    for (int k = 0; k < K; ++k) {
-      const int32_t s = slot_of[t * K + k];
-      if (s < 0 || s >= rows) continue;
-      uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<Ty*>(permuted) + static_cast<int64_t>(s) * D);
+    for (int k0 = 0; k0 < K; k0 += 8) {
+      int32_t slot[8];  // fetch the destinations together: one latency, not eight
 #pragma unroll
-      for (int v = 0; v < V; ++v)
-        if (col[v] < dvec) st_stream16(drow + col[v], val[v]);
+      for (int u = 0; u < 8; ++u) slot[u] = k0 + u < K ? slot_of[t * K + k0 + u] : -1;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (slot[u] < 0 || slot[u] >= rows) continue;
+        uint4* drow =
+            reinterpret_cast<uint4*>(reinterpret_cast<Ty*>(permuted) + static_cast<int64_t>(slot[u]) * D);
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+          if (col[v] < dvec) st_stream16(drow + col[v], val[v]);
+      }
     }
   }
 }
@@ -390,14 +372,6 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-static int64_t clamp_grid(int64_t items, int ctas_per_sm) {
-  int64_t grid = items;
-  if (ctas_per_sm > 0 && items > static_cast<int64_t>(kNumSMs) * ctas_per_sm)
-    grid = static_cast<int64_t>(kNumSMs) * ctas_per_sm;
-  if (grid > 0x7fffffffll) grid = 0x7fffffffll;
-  return grid;
-}
-
 }  // namespace fmoe
 
 using namespace fmoe;
@@ -414,7 +388,7 @@ extern "C" int fmoe_tune(const char* key, int value) {
                  "fmoe_tune: gather_threads must be a multiple of 32 in [0, 256]");
     g_gather_threads = value;
   } else if (k == "gather_ctas_per_sm") {
-    FMOE_REQUIRE(value >= 0 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: gather_ctas_per_sm in [0, 64]");
+    FMOE_REQUIRE(value >= -1 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: gather_ctas_per_sm in [-1, 64]");
     g_gather_ctas_per_sm = value;
   } else if (k == "bwd_ctas_per_sm") {
     FMOE_REQUIRE(value >= 1 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: bwd_ctas_per_sm in [1, 64]");
@@ -476,15 +450,18 @@ extern "C" int fmoe_combine_bwd(const void* plan, const void* grad_out, int64_t 
   // their gate gradient must still be defined
   if (grad_w != nullptr) FMOE_CUDA(cudaMemsetAsync(grad_w, 0, sizeof(float) * N, s));
   const int64_t dvec = D / kvec;
-  const TileCfg cfg = pick_tile(dvec, 1, 0, /*max_v=*/1);  // 8 rows x 1 vector in flight per thread
-  const int grid = static_cast<int>(clamp_grid(T, g_bwd_ctas_per_sm));
+  // tokens per CTA step: enough that the CTA's 8 warps each find a routed row
+  const int64_t avg_rows = T > 0 ? (N + T - 1) / T : 1;
+  int group = static_cast<int>(avg_rows >= kBwdWarps ? 1 : (kBwdWarps + avg_rows - 1) / (avg_rows > 0 ? avg_rows : 1));
+  if (group > kBwdWarps) group = kBwdWarps;
+  const int grid = static_cast<int>(clamp_grid((T + group - 1) / group, g_bwd_ctas_per_sm));
   int rc = 0;
-#define FMOE_BWD_LAUNCH(DT, V, GW)                                                              \
-  combine_bwd_kernel<DT, V, GW><<<grid, cfg.threads, 0, s>>>(                                   \
-      pv.seg_off, pv.row_of_slot, pv.src_sorted, pv.w_sorted, grad_out, grad_out_row_stride,    \
-      grad_rows, grad_w, T, D, dvec, cfg.tiles)
+#define FMOE_BWD_LAUNCH(DT, GW)                                                               \
+  combine_bwd_kernel<DT, GW><<<grid, kBwdWarps * 32, 0, s>>>(                                 \
+      pv.seg_off, pv.row_of_slot, pv.src_sorted, pv.w_sorted, grad_out, grad_out_row_stride,  \
+      grad_rows, grad_w, T, D, dvec, group)
   FMOE_DISPATCH_DTYPE(dtype, DT, {
-    if (grad_w) FMOE_BWD_LAUNCH(DT, 1, true); else FMOE_BWD_LAUNCH(DT, 1, false);
+    if (grad_w) FMOE_BWD_LAUNCH(DT, true); else FMOE_BWD_LAUNCH(DT, false);
     rc = check_launch("combine_bwd_kernel");
   });
 #undef FMOE_BWD_LAUNCH
@@ -518,7 +495,8 @@ extern "C" int fmoe_permute_fwd(const void* x, int64_t x_row_stride, const int32
   }
   const int64_t dvec = D / kvec;
   const TileCfg cfg = pick_tile(dvec, g_gather_v > 0 ? g_gather_v : 2, g_gather_threads);
-  const int grid = static_cast<int>(clamp_grid(T * cfg.tiles, g_gather_ctas_per_sm));
+  // one short-lived CTA per item measured 15% faster than a persistent grid for this write-heavy copy
+  const int grid = static_cast<int>(clamp_grid(T * cfg.tiles, g_gather_ctas_per_sm < 0 ? 0 : g_gather_ctas_per_sm));
 #define FMOE_PERM_LAUNCH(DT, V)                                                            \
   permute_fwd_kernel<DT, V><<<grid, cfg.threads, 0, s>>>(x, x_row_stride, slot_of, permuted, T, \
                                                          static_cast<int>(K), D, dvec, cfg.tiles)

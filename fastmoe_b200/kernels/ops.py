@@ -226,7 +226,6 @@ class CombinePlan:
 
 def build_combine_plan(expert_tensors, indices, weights, n_out, metadata=None) -> CombinePlan:
     """Builds the plan for out[n_out, D]. Four small launches on the current stream."""
-    global launch_count
     metadata = _metadata_for(expert_tensors, indices, metadata)
     ptr_table, chunk_sizes, expert_offsets, _, num_experts = metadata
     n_rows, dim, dtype = metadata.num_rows, metadata.dim, metadata.dtype
@@ -234,14 +233,13 @@ def build_combine_plan(expert_tensors, indices, weights, n_out, metadata=None) -
     device = indices.device
     nbytes = _lib.lib().fmoe_combine_plan_bytes(n_rows, n_out)
     buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
-    _lib.call(
-        "fmoe_combine_plan",
+    _call(
+        "fmoe_combine_plan", 4,
         ptr_table.data_ptr(), chunk_sizes.data_ptr(), expert_offsets.data_ptr(),
         indices.data_ptr(), _ITYPES[indices.dtype], weights.data_ptr(), _DTYPES[weights.dtype],
         num_experts, n_rows, n_out, dim, _DTYPES[dtype],
         buf.data_ptr(), nbytes, _status_word(device).data_ptr(), _stream_ptr(device),
     )  # fmt: skip
-    launch_count += 4
     return CombinePlan(buf, n_rows, n_out, dim, dtype, (expert_tensors, metadata, indices, weights))
 
 
@@ -255,15 +253,29 @@ def _check_out(out, dim, dtype, what="out"):
         raise ValueError(f"{what} must have unit column stride")
 
 
-# Benchmark hooks: number of kernels this module has launched, and (when set to a
-# list) a pair of CUDA events recorded around every gather launch.
+# Benchmark hooks: number of kernels this package has launched, and (when set to a
+# dict) per entry point a list of CUDA event pairs recorded around every call, on the
+# stream the kernels are launched on.
 launch_count = 0
 kernel_events = None
 
 
+def _call(fn_name, n_kernels, *args):
+    """Calls a C-ABI entry point; counts its kernels and, if asked, brackets it with events."""
+    global launch_count
+    launch_count += n_kernels
+    if kernel_events is None:
+        return _lib.call(fn_name, *args)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    rc = _lib.call(fn_name, *args)
+    ev1.record()
+    kernel_events.setdefault(fn_name, []).append((ev0, ev1))
+    return rc
+
+
 def _combine_into(expert_tensors, indices, weights, out, metadata, accumulate, mode=None):
     """Runs the combine into `out` ([T, D], any row stride). Returns the plan (or None)."""
-    global launch_count
     mode = _mode if mode is None else mode
     metadata = _metadata_for(expert_tensors, indices, metadata)
     dim, dtype = metadata.dim, metadata.dtype
@@ -273,17 +285,10 @@ def _combine_into(expert_tensors, indices, weights, out, metadata, accumulate, m
     row_stride = int(out.stride(0)) if n_out > 1 else dim
     if mode == "gather":
         plan = build_combine_plan(expert_tensors, indices, weights, n_out, metadata)
-        if kernel_events is not None:
-            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            ev0.record()
-        _lib.call(
-            "fmoe_combine_gather", plan.buf.data_ptr(), out.data_ptr(), row_stride, plan.n_rows,
+        _call(
+            "fmoe_combine_gather", 1, plan.buf.data_ptr(), out.data_ptr(), row_stride, plan.n_rows,
             n_out, dim, _DTYPES[dtype], 1 if accumulate else 0, _stream_ptr(device),
         )  # fmt: skip
-        if kernel_events is not None:
-            ev1.record()
-            kernel_events.append((ev0, ev1))
-        launch_count += 1
         _maybe_check(device, "grouped_weighted_scatter_add")
         return plan
     ptr_table, chunk_sizes, expert_offsets, _, num_experts = metadata
@@ -291,14 +296,13 @@ def _combine_into(expert_tensors, indices, weights, out, metadata, accumulate, m
     indices, weights = _check_routing(indices, weights, n_rows)
     if not accumulate:
         out.zero_()
-    _lib.call(
-        "fmoe_combine_scatter",
+    _call(
+        "fmoe_combine_scatter", 1,
         ptr_table.data_ptr(), chunk_sizes.data_ptr(), expert_offsets.data_ptr(),
         indices.data_ptr(), _ITYPES[indices.dtype], weights.data_ptr(), _DTYPES[weights.dtype],
         out.data_ptr(), row_stride, num_experts, n_rows, n_out, dim, _DTYPES[dtype],
         _status_word(device).data_ptr(), _stream_ptr(device),
     )  # fmt: skip
-    launch_count += 1
     _maybe_check(device, "grouped_weighted_scatter_add")
     return None
 
@@ -343,10 +347,8 @@ class GroupedWeightedScatterAdd(torch.autograd.Function):
         want_gw = ctx.needs_input_grad[1]
         grad_w = torch.empty(n_rows, device=device, dtype=torch.float32) if want_gw else None
         row_stride = int(grad_output.stride(0)) if grad_output.shape[0] > 1 else dim
-        global launch_count
-        launch_count += 1
-        _lib.call(
-            "fmoe_combine_bwd", plan.buf.data_ptr(), grad_output.data_ptr(), row_stride,
+        _call(
+            "fmoe_combine_bwd", 1, plan.buf.data_ptr(), grad_output.data_ptr(), row_stride,
             grad_rows.data_ptr(), grad_w.data_ptr() if want_gw else None, n_rows, plan.n_out, dim,
             _DTYPES[plan.dtype], _stream_ptr(device),
         )  # fmt: skip

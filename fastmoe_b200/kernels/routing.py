@@ -45,11 +45,10 @@ class _RouteTopK(torch.autograd.Function):
         T, E = logits.shape
         topk_idx = torch.empty(T, K, dtype=torch.int64, device=logits.device)
         topk_w = torch.empty(T, K, dtype=w_dtype, device=logits.device)
-        _lib.call(
-            "fmoe_route_topk", logits.data_ptr(), _DTYPES[logits.dtype], T, E, K,
+        ops._call(
+            "fmoe_route_topk", 1, logits.data_ptr(), _DTYPES[logits.dtype], T, E, K,
             topk_idx.data_ptr(), topk_w.data_ptr(), _DTYPES[w_dtype], _stream_ptr(logits.device),
         )  # fmt: skip
-        ops.launch_count += 1
         ctx.save_for_backward(topk_w, topk_idx)
         ctx.shape, ctx.logits_dtype = (T, E), logits.dtype
         ctx.mark_non_differentiable(topk_idx)
@@ -92,13 +91,12 @@ class _BuildIndex(torch.autograd.Function):
         slot_of = torch.empty(N, dtype=torch.int32, device=dev)
         nbytes = _lib.lib().fmoe_build_index_bytes(T, E, K)
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-        _lib.call(
-            "fmoe_build_index", topk_idx.data_ptr(), topk_w.data_ptr(), _DTYPES[topk_w.dtype], T, E, K,
+        ops._call(
+            "fmoe_build_index", 3, topk_idx.data_ptr(), topk_w.data_ptr(), _DTYPES[topk_w.dtype], T, E, K,
             world, reverse_map.data_ptr(), sorted_w.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
             rank_counts.data_ptr(), slot_of.data_ptr(), scratch.data_ptr(), nbytes,
             _status_word(dev).data_ptr(), _stream_ptr(dev),
         )  # fmt: skip
-        ops.launch_count += 3
         ctx.save_for_backward(slot_of)
         ctx.shape = (T, K)
         ctx.mark_non_differentiable(reverse_map, counts, offsets, rank_counts, slot_of)
@@ -133,11 +131,10 @@ class _PermuteRows(torch.autograd.Function):
             raise ValueError("slot_of must be int32 with T*K entries")
         out = torch.empty(T * K, D, dtype=x.dtype, device=x.device)
         row_stride = int(x.stride(0)) if T > 1 else D
-        _lib.call(
-            "fmoe_permute_fwd", x.data_ptr(), row_stride, slot_of.data_ptr(), out.data_ptr(), T, K, D,
+        ops._call(
+            "fmoe_permute_fwd", 1, x.data_ptr(), row_stride, slot_of.data_ptr(), out.data_ptr(), T, K, D,
             _DTYPES[x.dtype], _stream_ptr(x.device),
         )  # fmt: skip
-        ops.launch_count += 1
         ctx.save_for_backward(slot_of)
         ctx.dims = (T, K, D)
         return out
@@ -148,11 +145,10 @@ class _PermuteRows(torch.autograd.Function):
         T, K, D = ctx.dims
         grad_out = grad_out.contiguous()
         grad_x = torch.empty(T, D, dtype=grad_out.dtype, device=grad_out.device)
-        _lib.call(
-            "fmoe_permute_bwd", grad_out.data_ptr(), slot_of.data_ptr(), grad_x.data_ptr(), D, T, K, D,
+        ops._call(
+            "fmoe_permute_bwd", 1, grad_out.data_ptr(), slot_of.data_ptr(), grad_x.data_ptr(), D, T, K, D,
             _DTYPES[grad_out.dtype], _stream_ptr(grad_out.device),
         )  # fmt: skip
-        ops.launch_count += 1
         return grad_x, None, None
 
 

@@ -63,8 +63,8 @@ const char* fmoe_status_name(int status);
 /* Launch-shape knobs for benchmark sweeps; process-wide, not thread-safe against
  * concurrent launches. Keys: "gather_v" (16-byte vectors per thread: 0 = auto,
  * 1, 2, 4), "gather_threads" (threads per CTA, 0 = auto, else a multiple of 32
- * up to 256), "gather_ctas_per_sm" (0 = one CTA per work item, else a
- * persistent grid of 148 x value CTAs), "bwd_ctas_per_sm". */
+ * up to 256), "gather_ctas_per_sm" (-1 = auto, 0 = one CTA per work item,
+ * else a persistent grid of 148 x value CTAs), "bwd_ctas_per_sm". */
 int fmoe_tune(const char* key, int value);
 
 /* ---- combine: scatter form ---------------------------------------------- */
