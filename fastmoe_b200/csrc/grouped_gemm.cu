@@ -1,0 +1,418 @@
+// Grouped GEMM for the expert FFN on the 5th-generation tensor cores (tcgen05):
+//   C[rows of expert e, :] = A[rows of expert e, :] x W_e^T        (plain)
+//   C[rows of expert e, :] = silu(A W_gate_e^T) * (A W_up_e^T)     (SwiGLU, fused epilogue)
+// A is [R, K] bf16 with each expert's rows contiguous (offsets/counts on the device, as
+// the index builder leaves them), W is [E, N, K] bf16 in nn.Linear layout. Replaces the
+// Python loop of per-expert cuBLAS GEMMs in MoEFeedForward.compute_experts of
+// polkadot21/fastmoe (src/fastmoe/models/tiny_model.py:282-294): one persistent launch,
+// ragged M per expert resolved on the device, no host knowledge of the counts.
+//
+// Structure per CTA (192 threads, one CTA per SM):
+//   warp 0      TMA producer: A tile 128x64 and W tile 256x64 (two 128-row boxes) per stage,
+//               128-byte swizzle, 4 stages, mbarrier full/empty pairs
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16, bf16 -> fp32)
+//               into one of two 256-column TMEM accumulators; tcgen05.commit frees stages
+//   warps 2-5   epilogue: tcgen05.ld of the finished accumulator (row = TMEM lane),
+//               activation, bf16 rounding, masked stores of the expert's valid rows; runs
+//               while the next tile's MMAs fill the other accumulator
+// Every mbarrier wait is bounded: on a timeout the kernel sets FMOE_STATUS_WAIT_TIMEOUT in
+// the status word, every role leaves its loop, TMEM is released and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace fmoe {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4, kUmmaK = 16;
+constexpr int kABytes = kBM * kBK * 2;        // 16 KB
+constexpr int kBBytes = kBN * kBK * 2;        // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kGemmThreads = 192;
+constexpr int kMaxExperts = 1024;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+struct GemmArgs {
+  const int64_t* offsets;  // [E] first row of each expert in A / C
+  const int64_t* counts;   // [E] rows of each expert
+  __nv_bfloat16* C;
+  int64_t ldc;             // row stride of C in elements
+  int64_t R;               // rows of A
+  int E;
+  int n_blocks;            // column tiles per expert
+  int k_blocks;            // K / 64
+  int w_rows_per_expert;   // rows of the weight tensor per expert (N, or 2*ff for SwiGLU)
+  int up_row_offset;       // SwiGLU: row of the first "up" weight inside an expert (= ff), else 128
+  int swiglu;
+  int32_t* status;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// Bounded wait: false after kSpinLimit unsuccessful probes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spin & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile, 128-byte swizzle, rows 128 bytes apart,
+// 8-row groups 1024 bytes apart (the layout a 128B-swizzled TMA box produces).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr >> 4) & 0x3fff);        // start address
+  d |= static_cast<uint64_t>(1) << 16;                       // leading byte offset (unused here)
+  d |= static_cast<uint64_t>((1024 >> 4) & 0x3fff) << 32;    // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                       // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                       // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: D fp32, A and B bf16, both K-major, M=128, N=256.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+struct TileCoord {
+  int expert, mb, nb, rows;  // rows = valid rows of this M block
+  int64_t row0;              // first row in A / C
+};
+
+// Tiles are numbered expert-major, then column block, then row block: the row blocks that
+// share a weight tile are neighbours and run at the same time, so the weight tile comes
+// from DRAM once and from L2 afterwards.
+__device__ __forceinline__ TileCoord locate_tile(int tile, const int* mb_prefix, const GemmArgs& a) {
+  int lo = 0, hi = a.E;  // last e with mb_prefix[e] * n_blocks <= tile
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (static_cast<int64_t>(mb_prefix[mid]) * a.n_blocks <= tile) lo = mid; else hi = mid;
+  }
+  TileCoord c;
+  c.expert = lo;
+  const int mblocks = mb_prefix[lo + 1] - mb_prefix[lo];
+  const int local = tile - mb_prefix[lo] * a.n_blocks;
+  c.nb = local / mblocks;
+  c.mb = local - c.nb * mblocks;
+  c.row0 = a.offsets[lo] + static_cast<int64_t>(c.mb) * kBM;
+  const int64_t left = a.counts[lo] - static_cast<int64_t>(c.mb) * kBM;
+  c.rows = static_cast<int>(left < kBM ? left : kBM);
+  return c;
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                        const GemmArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + kStages * kABytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty = full + kStages;
+  uint64_t* tmem_full = empty + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  int* abort_flag = reinterpret_cast<int*>(tmem_base_slot + 1);
+  int* mb_prefix = abort_flag + 1;  // [E + 1]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- set-up: tile table, barriers, TMEM ----------------------------------------------
+  for (int e = threadIdx.x; e < a.E; e += kGemmThreads) {
+    const int64_t n = a.counts[e];
+    mb_prefix[e + 1] = static_cast<int>((n + kBM - 1) / kBM);
+  }
+  if (threadIdx.x == 0) {
+    mb_prefix[0] = 0;
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0) {  // inclusive scan of the per-expert block counts, 32 at a time
+    int carry = 0;
+    for (int base = 0; base < a.E; base += 32) {
+      const int e = base + lane;
+      int v = e < a.E ? mb_prefix[e + 1] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += n;
+      }
+      if (e < a.E) mb_prefix[e + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  if (warp == 1) {  // the MMA warp owns the tensor memory: all 512 columns, two accumulators
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_base_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int total_tiles = mb_prefix[a.E] * a.n_blocks;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer ---------------------------------------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const TileCoord c = locate_tile(tile, mb_prefix, a);
+      const int w_row0 = c.expert * a.w_rows_per_expert + c.nb * (a.swiglu ? 128 : kBN);
+      const int w_row1 = w_row0 + a.up_row_offset;
+      for (int kb = 0; kb < a.k_blocks; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) goto timed_out;
+        mbar_expect_tx(&full[stage], kStageBytes);
+        tma_load_2d(smem_a + stage * kABytes, &map_a, kb * kBK, static_cast<int>(c.row0), &full[stage]);
+        tma_load_2d(smem_b + stage * kBBytes, &map_w, kb * kBK, w_row0, &full[stage]);
+        tma_load_2d(smem_b + stage * kBBytes + kBBytes / 2, &map_w, kb * kBK, w_row1, &full[stage]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer -----------------------------------------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) goto timed_out;
+      tcgen05_fence_after();
+      const uint32_t tmem_d = tmem_base + acc * kBN;
+      for (int kb = 0; kb < a.k_blocks; ++kb) {
+        if (!mbar_wait(&full[stage], phase, abort_flag)) goto timed_out;
+        tcgen05_fence_after();
+        const uint64_t da = smem_desc(smem_u32(smem_a + stage * kABytes));
+        const uint64_t db = smem_desc(smem_u32(smem_b + stage * kBBytes));
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          // 16 bf16 = 32 bytes along K inside the swizzle atom: +2 in the encoded address
+          umma_bf16(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&empty[stage]);  // frees the stage when these MMAs have read it
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      umma_commit(&tmem_full[acc]);  // accumulator complete
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue -------------------------------------------------------------------
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read: 32*quarter .. +31
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const TileCoord c = locate_tile(tile, mb_prefix, a);
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) goto timed_out;
+      tcgen05_fence_after();
+      const int row = quarter * 32 + lane;
+      const bool valid = row < c.rows;
+      const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (a.swiglu) {
+        __nv_bfloat16* crow = a.C + (c.row0 + row) * a.ldc + static_cast<int64_t>(c.nb) * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + c0, g);
+          tmem_ld32(taddr + 128 + c0, u);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                f[i] = silu(__uint_as_float(g[8 * v + i])) * __uint_as_float(u[8 * v + i]);
+              *reinterpret_cast<uint4*>(crow + c0 + 8 * v) = pack16<FMOE_BF16>(f);
+            }
+          }
+        }
+      } else {
+        __nv_bfloat16* crow = a.C + (c.row0 + row) * a.ldc + static_cast<int64_t>(c.nb) * kBN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * v + i]);
+              *reinterpret_cast<uint4*>(crow + c0 + 8 * v) = pack16<FMOE_BF16>(f);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);  // this warp is done with the accumulator
+    }
+  }
+  goto done;
+
+timed_out:
+  *abort_flag = 1;
+  if (a.status != nullptr) atomicOr(a.status, FMOE_STATUS_WAIT_TIMEOUT);
+
+done:
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major tensor [rows, cols], box = 64 columns x 128 rows, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, const char* what) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  FMOE_REQUIRE(fn != nullptr, FMOE_ERR_DEVICE, "fmoe_grouped_gemm: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {kBK, 128};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FMOE_REQUIRE(r == CUDA_SUCCESS, FMOE_ERR_ARG, "fmoe_grouped_gemm: cuTensorMapEncodeTiled(%s) failed with %d", what,
+               static_cast<int>(r));
+  return FMOE_OK;
+}
+
+}  // namespace fmoe
+
+using namespace fmoe;
+
+extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
+                                 const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
+                                 int swiglu, int32_t* status, void* stream) {
+  FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm: bad sizes");
+  FMOE_REQUIRE(E <= kMaxExperts, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: supports E <= %d", kMaxExperts);
+  FMOE_REQUIRE(K % kBK == 0, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: K=%lld must be a multiple of %d",
+               (long long)K, kBK);
+  if (swiglu) {
+    FMOE_REQUIRE(N % 256 == 0, FMOE_ERR_UNSUPPORTED,
+                 "fmoe_grouped_gemm: SwiGLU needs N = 2*ff with ff a multiple of 128 (N=%lld)", (long long)N);
+  } else {
+    FMOE_REQUIRE(N % kBN == 0, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: N=%lld must be a multiple of %d",
+                 (long long)N, kBN);
+  }
+  FMOE_REQUIRE(R < (1ll << 31) && E * N < (1ll << 31), FMOE_ERR_UNSUPPORTED,
+               "fmoe_grouped_gemm: R and E*N must fit in int32");
+  if (E == 0 || R == 0) return FMOE_OK;
+  FMOE_REQUIRE(a && w && c && offsets && counts, FMOE_ERR_ARG, "fmoe_grouped_gemm: null pointer argument");
+  FMOE_REQUIRE(aligned_to(a, 16) && aligned_to(w, 16) && aligned_to(c, 16), FMOE_ERR_ARG,
+               "fmoe_grouped_gemm: a, w and c must be 16-byte aligned");
+  CUtensorMap map_a, map_w;
+  int rc = make_map(&map_a, a, R, K, "A");
+  if (rc != 0) return rc;
+  rc = make_map(&map_w, w, E * N, K, "W");
+  if (rc != 0) return rc;
+
+  GemmArgs g;
+  g.offsets = offsets;
+  g.counts = counts;
+  g.C = static_cast<__nv_bfloat16*>(c);
+  g.ldc = swiglu ? N / 2 : N;
+  g.R = R;
+  g.E = static_cast<int>(E);
+  g.n_blocks = static_cast<int>(swiglu ? (N / 2) / 128 : N / kBN);
+  g.k_blocks = static_cast<int>(K / kBK);
+  g.w_rows_per_expert = static_cast<int>(N);
+  g.up_row_offset = static_cast<int>(swiglu ? N / 2 : 128);
+  g.swiglu = swiglu ? 1 : 0;
+  g.status = status;
+
+  const size_t smem = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + sizeof(int) * (E + 2);
+  // per device and cheap: set on every call rather than caching per device
+  FMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 1024 + kStages * kStageBytes + 256 + static_cast<int>(sizeof(int)) * (kMaxExperts + 2)));
+  // upper bound of the tile count, known without reading the counts: one partial block per expert
+  const int64_t max_tiles = (R / kBM + E) * g.n_blocks;
+  const int grid = static_cast<int>(max_tiles < kNumSMs ? max_tiles : kNumSMs);
+  grouped_gemm_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(map_a, map_w, g);
+  return check_launch("grouped_gemm_kernel");
+}

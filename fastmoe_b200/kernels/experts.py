@@ -1,0 +1,93 @@
+"""Expert FFN as grouped GEMMs on the tcgen05 tensor cores.
+
+`grouped_gemm` multiplies every expert's contiguous block of rows by that expert's
+weight matrix in ONE persistent launch, reading the per-expert row ranges from device
+memory, and `grouped_swiglu_ffn` chains two of them into down(silu(gate(x)) * up(x)).
+They replace the Python loop over `self.experts` in `MoEFeedForward.compute_experts` of
+polkadot21/fastmoe (src/fastmoe/models/tiny_model.py:282-294).
+
+Forward runs on the hand-written kernel (`csrc/grouped_gemm.cu`). The backward pass is
+composed from per-expert matrix products through torch (library GEMMs) and needs the
+counts on the host.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from . import ops
+from .ops import _require_cuda, _status_word, _stream_ptr
+
+
+def _check(a, w, offsets, counts):
+    _require_cuda(a, "a")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise ValueError("grouped_gemm runs in bfloat16")
+    if a.dim() != 2 or w.dim() != 3 or w.shape[2] != a.shape[1]:
+        raise ValueError(f"a must be [R, K] and w [E, N, K]; got {tuple(a.shape)} and {tuple(w.shape)}")
+    if offsets.dtype != torch.int64 or counts.dtype != torch.int64:
+        raise ValueError("offsets and counts must be int64 device tensors")
+    if offsets.numel() != w.shape[0] or counts.numel() != w.shape[0]:
+        raise ValueError("offsets and counts need one entry per expert")
+
+
+def _launch(a, w, offsets, counts, swiglu):
+    a, w = a.contiguous(), w.contiguous()
+    R, K = a.shape
+    E, N, _ = w.shape
+    cols = N // 2 if swiglu else N
+    # rows that belong to no expert are never written: start from zeros so they are defined
+    c = torch.zeros(R, cols, dtype=torch.bfloat16, device=a.device) if R else a.new_empty(0, cols)
+    ops._call(
+        "fmoe_grouped_gemm", 1, a.data_ptr(), w.data_ptr(), c.data_ptr(), offsets.data_ptr(),
+        counts.data_ptr(), E, R, N, K, 1 if swiglu else 0, _status_word(a.device).data_ptr(),
+        _stream_ptr(a.device),
+    )  # fmt: skip
+    return c
+
+
+class _GroupedGemm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, w, offsets, counts, swiglu):
+        _check(a, w, offsets, counts)
+        ctx.save_for_backward(a, w, offsets, counts)
+        ctx.swiglu = swiglu
+        return _launch(a, w, offsets, counts, swiglu)
+
+    @staticmethod
+    def backward(ctx, grad_c):
+        a, w, offsets, counts = ctx.saved_tensors
+        offs, cnts = offsets.tolist(), counts.tolist()
+        grad_a = torch.zeros_like(a)
+        grad_w = torch.zeros_like(w)
+        ff = w.shape[1] // 2
+        for e, (o, n) in enumerate(zip(offs, cnts)):
+            if n == 0:
+                continue
+            x, g = a[o : o + n], grad_c[o : o + n]
+            if ctx.swiglu:
+                h = (x @ w[e].t()).float()
+                gate, up = h[:, :ff], h[:, ff:]
+                sig = torch.sigmoid(gate)
+                d_gate = g.float() * up * sig * (1 + gate * (1 - sig))
+                d_up = g.float() * gate * sig
+                g = torch.cat([d_gate, d_up], dim=1).to(a.dtype)
+            grad_a[o : o + n] = g @ w[e]
+            grad_w[e] = g.t() @ x
+        return grad_a, grad_w, None, None, None
+
+
+def grouped_gemm(a, w, offsets, counts, swiglu=False):
+    """C[rows of e] = A[rows of e] @ w[e].T (or the fused SwiGLU of its two halves).
+
+    a [R, K] bf16; w [E, N, K] bf16; offsets, counts int64 [E] on the device (rows
+    [offsets[e], offsets[e]+counts[e]) belong to expert e). Returns bf16 [R, N] (or [R, N/2]).
+    """
+    return _GroupedGemm.apply(a, w, offsets, counts, bool(swiglu))
+
+
+def grouped_swiglu_ffn(x, w_gate_up, w_down, offsets, counts):
+    """down(silu(gate(x)) * up(x)) per expert. w_gate_up [E, 2*ff, D] (gate rows first), w_down [E, D, ff]."""
+    hidden = grouped_gemm(x, w_gate_up, offsets, counts, swiglu=True)
+    return grouped_gemm(hidden, w_down, offsets, counts, swiglu=False)

@@ -213,6 +213,24 @@ int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_of, void* gr
                      int64_t grad_x_row_stride, int64_t T, int64_t K, int64_t D,
                      int dtype, void* stream);
 
+/* ---- expert FFN: grouped GEMM on tcgen05 ------------------------------------------ */
+/*
+ * For every expert e with rows [offsets[e], offsets[e] + counts[e]) of A:
+ *   swiglu = 0:  C[rows, :N]   = A[rows, :K] x W[e]^T                       W[e] is [N, K]
+ *   swiglu = 1:  C[rows, :N/2] = silu(A x Wg[e]^T) * (A x Wu[e]^T)          W[e] = [Wg; Wu], each [N/2, K]
+ * A [R, K], W [E, N, K], C bf16 row-major; offsets/counts int64[E] ON THE DEVICE (the index
+ * builder's output: the host never learns the counts). fp32 accumulation in tensor
+ * memory, one rounding to bf16. K must be a multiple of 64, N of 256, E <= 1024.
+ * Replaces the per-expert Python loop of cuBLAS GEMMs in MoEFeedForward.compute_experts
+ * (src/fastmoe/models/tiny_model.py:282-294; the reference's experts are
+ * Linear-GELU-Linear, tiny_model.py:68-77; SwiGLU is what the expert-parallel benchmark
+ * configuration asks for). Rows of A outside every expert's range are not touched in C.
+ * A bounded device-side wait that gives up sets FMOE_STATUS_WAIT_TIMEOUT in `status`.
+ */
+int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
+                      const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
+                      int swiglu, int32_t* status, void* stream);
+
 /* ---- host-buffer call -------------------------------------------------------- */
 /*
  * The whole combine for a caller that holds HOST memory: copies the E expert
