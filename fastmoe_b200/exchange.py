@@ -56,6 +56,7 @@ class SplitList(list):
     to_expert_major = None  # int64 [R]: expert-major row i comes from rank-major row to_expert_major[i]
     to_rank_major = None  # its inverse
     counts_by_source = None  # int64 [world, E_local] on the host side as nested lists
+    device_counts = None  # the same counts as an int64 device tensor, when one exists
 
 
 def exchange_counts(send_expert_counts: torch.Tensor, send_rank_counts: torch.Tensor, group=None):

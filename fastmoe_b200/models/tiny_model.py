@@ -29,6 +29,7 @@ from torch.profiler import record_function
 
 from .. import consts, exchange
 from ..kernels import routing
+from ..kernels.experts import grouped_swiglu_ffn
 from ..kernels.ops import grouped_weighted_scatter_add
 
 
@@ -50,17 +51,40 @@ class MultiheadSelfAttention(nn.Module):
         return self.proj(y.transpose(1, 2).reshape(B, T, D))
 
 
-class SwiGLUExpert(nn.Module):
-    """down(silu(gate(x)) * up(x)), bias-free."""
+class GroupedSwiGLUExperts(nn.Module):
+    """All local SwiGLU experts as two stacked weight tensors, the layout the grouped GEMM
+    reads: `w_gate_up` [E, 2*ff, D] (gate rows, then up rows) and `w_down` [E, D, ff],
+    bias-free. Iterating or indexing yields one callable per expert that computes
+    down(silu(gate(x)) * up(x)) with plain matrix products."""
 
-    def __init__(self, dim, ff_dim):
+    def __init__(self, num_experts, dim, ff_dim):
         super().__init__()
-        self.gate = nn.Linear(dim, ff_dim, bias=False)
-        self.up = nn.Linear(dim, ff_dim, bias=False)
-        self.down = nn.Linear(ff_dim, dim, bias=False)
+        self.num_experts, self.dim, self.ff_dim = num_experts, dim, ff_dim
+        self.w_gate_up = nn.Parameter(torch.empty(num_experts, 2 * ff_dim, dim))
+        self.w_down = nn.Parameter(torch.empty(num_experts, dim, ff_dim))
+        for w in (self.w_gate_up, self.w_down):  # nn.Linear's default range, without a 22 GB temporary
+            bound = 1.0 / w.shape[-1] ** 0.5
+            nn.init.uniform_(w, -bound, bound)
 
-    def forward(self, x):
-        return self.down(F.silu(self.gate(x)) * self.up(x))
+    def __len__(self):
+        return self.num_experts
+
+    def expert(self, e):
+        def run(x):
+            h = x @ self.w_gate_up[e].t()
+            return (F.silu(h[:, : self.ff_dim]) * h[:, self.ff_dim :]) @ self.w_down[e].t()
+
+        return run
+
+    def __getitem__(self, e):
+        return self.expert(e)
+
+    def __iter__(self):
+        return (self.expert(e) for e in range(self.num_experts))
+
+    def forward(self, x, offsets, counts):
+        """x rows grouped by expert (device-side `offsets`/`counts`, int64 [E]) -> FFN output rows."""
+        return grouped_swiglu_ffn(x, self.w_gate_up, self.w_down, offsets, counts)
 
 
 class MoEFeedForward(nn.Module):
@@ -76,15 +100,16 @@ class MoEFeedForward(nn.Module):
             raise ValueError(f"num_experts={num_experts} is not divisible by world size {self.world_size}")
         self.num_local_experts = num_experts // self.world_size
         self.router = nn.Linear(dim, num_experts, bias=False)
+        self.expert_type = expert_type
         if expert_type == "gelu":
-            make = lambda: nn.Sequential(  # noqa: E731
-                nn.Linear(dim, ff_dim, bias=False), nn.GELU(), nn.Linear(ff_dim, dim, bias=False)
+            self.experts = nn.ModuleList(
+                nn.Sequential(nn.Linear(dim, ff_dim, bias=False), nn.GELU(), nn.Linear(ff_dim, dim, bias=False))
+                for _ in range(self.num_local_experts)
             )
         elif expert_type == "swiglu":
-            make = lambda: SwiGLUExpert(dim, ff_dim)  # noqa: E731
+            self.experts = GroupedSwiGLUExperts(self.num_local_experts, dim, ff_dim)
         else:
             raise ValueError(f"expert_type must be 'gelu' or 'swiglu', got {expert_type!r}")
-        self.experts = nn.ModuleList([make() for _ in range(self.num_local_experts)])
 
     # -- stage 1 ---------------------------------------------------------------------------
     def gate_and_sort(self, x):
@@ -111,7 +136,9 @@ class MoEFeedForward(nn.Module):
         tokens_per_local_expert). One host synchronisation (the counts).
         """
         if self.world_size == 1:
-            counts = send_expert_counts.view(-1).tolist()
+            device_counts = send_expert_counts.view(-1)
+            counts = exchange.SplitList(device_counts.tolist())
+            counts.device_counts = device_counts
             total = [sum(counts)]
             return permuted_data, total, list(total), counts
         _, nested, send_list, recv_list = exchange.exchange_counts(send_expert_counts, send_rank_counts, self.group)
@@ -121,6 +148,7 @@ class MoEFeedForward(nn.Module):
         splits.to_expert_major, splits.to_rank_major, splits.counts_by_source = to_expert_major, to_rank_major, nested
         if self.num_local_experts > 1:
             recv = recv.index_select(0, to_expert_major)
+        tokens_per_expert = exchange.SplitList(tokens_per_expert)
         return recv, splits, send_list, tokens_per_expert
 
     # -- stage 3 ---------------------------------------------------------------------------
@@ -131,8 +159,23 @@ class MoEFeedForward(nn.Module):
             outs.append(expert(chunk) if chunk.shape[0] > 0 else chunk.new_empty(0, self.dim))
         return outs
 
+    def _grouped_ffn(self, recv_data, tokens_per_expert):
+        """SwiGLU experts on the FAST path: two grouped-GEMM launches, no per-expert loop."""
+        counts = getattr(tokens_per_expert, "device_counts", None)
+        if counts is None:
+            staging = torch.tensor(list(tokens_per_expert), dtype=torch.int64, pin_memory=True)
+            counts = staging.to(recv_data.device, non_blocking=True)
+        offsets = torch.cumsum(counts, 0) - counts
+        return self.experts(recv_data, offsets, counts)
+
+    def _use_grouped(self, recv_data):
+        return (self.expert_type == "swiglu" and self.implementation == consts.MoEImplementation.FAST
+                and recv_data.dtype == torch.bfloat16)  # fmt: skip
+
     def compute_experts(self, recv_data, tokens_per_expert):
         """Concatenated expert outputs, rows in the order of recv_data (tiny_model.py:282-294)."""
+        if self._use_grouped(recv_data):
+            return self._grouped_ffn(recv_data, tokens_per_expert)
         outs = self.expert_outputs(recv_data, tokens_per_expert)
         return torch.cat(outs, dim=0) if outs else recv_data.new_empty(0, self.dim)
 
@@ -167,7 +210,8 @@ class MoEFeedForward(nn.Module):
         recv, recv_splits, send_splits, tokens_per_expert = self.dispatch_exchange(
             permuted, send_rank_counts, send_exp_counts
         )
-        if self.world_size == 1 and self.implementation == consts.MoEImplementation.FAST:
+        if (self.world_size == 1 and self.implementation == consts.MoEImplementation.FAST
+                and not self._use_grouped(recv)):  # fmt: skip
             # "no-cat": the combine reads the disjoint expert outputs through its pointer table
             return self.unpermute(self.expert_outputs(recv, tokens_per_expert), rev_idx, weights, shape)
         expert_out = self.compute_experts(recv, tokens_per_expert)
@@ -205,40 +249,66 @@ class PipelinedMoEBlock(nn.Module):
         chunks = x.chunk(self.num_micro_batches, dim=0)
         streams = self._streams(len(chunks))
         main = torch.cuda.current_stream()
-        state = [dict() for _ in chunks]
+        resid, moe_in = [], []
         prev_attn_done = None
-        # phase A: attention + gate + dispatch per micro-batch, staggered so that micro-batch
-        # i+1's attention overlaps micro-batch i's exchange
+        # attention per micro-batch, staggered: micro-batch i+1's attention overlaps i's exchange
         for i, (mb, s) in enumerate(zip(chunks, streams)):
             s.wait_stream(main)
             with torch.cuda.stream(s):
                 if prev_attn_done is not None:
                     s.wait_event(prev_attn_done)
                 with record_function(f"S{i}: Attn {i}"):
-                    resid = mb + self.attn(self.norm1(mb))
-                    gated = self.moe.gate_and_sort(self.norm2(resid))
+                    r = mb + self.attn(self.norm1(mb))
+                    resid.append(r)
+                    moe_in.append(self.norm2(r))
                 prev_attn_done = torch.cuda.Event()
                 prev_attn_done.record()
-                state[i].update(resid=resid, gated=gated)
-        for i, s in enumerate(streams[: len(chunks)]):
-            with torch.cuda.stream(s):
-                perm, rank_counts, exp_counts, rev, w, shape = state[i]["gated"]
-                with record_function(f"S{i}: Dispatch {i}"):
-                    state[i]["dispatched"] = self.moe.dispatch_exchange(perm, rank_counts, exp_counts)
-        # phase B: experts, return exchange and combine per micro-batch
+        moe_out = pipelined_moe_forward(self.moe, moe_in, streams)
         outs = []
-        for i, s in enumerate(streams[: len(chunks)]):
+        for i, s in enumerate(streams):
             with torch.cuda.stream(s):
-                _, _, _, rev, w, shape = state[i]["gated"]
-                recv, recv_splits, send_splits, tokens = state[i]["dispatched"]
-                with record_function(f"S{i}: Experts {i}"):
-                    eo = self.moe.compute_experts(recv, tokens)
-                with record_function(f"S{i}: Combine {i}"):
-                    fd = self.moe.combine_exchange(eo, recv_splits, send_splits)
-                with record_function(f"S{i}: Finalize {i}"):
-                    y = self.moe.unpermute(fd, rev, w, shape) + state[i]["resid"]
-                    y.record_stream(main)  # read by the concatenation on the caller's stream
-                    outs.append(y)
-        for s in streams[: len(chunks)]:
+                y = moe_out[i] + resid[i]
+                y.record_stream(main)  # read by the concatenation on the caller's stream
+                outs.append(y)
             main.wait_stream(s)
         return torch.cat(outs, dim=0)
+
+
+def pipelined_moe_forward(moe, inputs, streams):
+    """Runs `moe` on several micro-batches, one CUDA stream each, issuing the work so that
+    the token exchange of micro-batch i+1 is in flight while micro-batch i's experts compute:
+
+        gate(0..n-1) ; dispatch(0) ; for i: dispatch(i+1), experts(i), combine(i)
+
+    (the software-pipelined form of the two-stream zig-zag of polkadot21/fastmoe,
+    src/fastmoe/models/tiny_model.py:506-630, for any number of micro-batches). Collectives
+    of one process group execute in issue order, which is why dispatch(i+1) is issued before
+    combine(i). Returns the per-micro-batch outputs, each produced on its own stream.
+    """
+    n = len(inputs)
+    gated, dispatched, outs = [None] * n, [None] * n, [None] * n
+    for i in range(n):
+        with torch.cuda.stream(streams[i]), record_function(f"S{i}: Gate {i}"):
+            gated[i] = moe.gate_and_sort(inputs[i])
+
+    def dispatch(i):
+        with torch.cuda.stream(streams[i]), record_function(f"S{i}: Dispatch {i}"):
+            perm, rank_counts, exp_counts, _, _, _ = gated[i]
+            dispatched[i] = moe.dispatch_exchange(perm, rank_counts, exp_counts)
+
+    if n:
+        dispatch(0)
+    for i in range(n):
+        if i + 1 < n:
+            dispatch(i + 1)
+        with torch.cuda.stream(streams[i]):
+            _, _, _, rev, w, shape = gated[i]
+            recv, recv_splits, send_splits, tokens = dispatched[i]
+            with record_function(f"S{i}: Experts {i}"):
+                eo = moe.compute_experts(recv, tokens)
+            with record_function(f"S{i}: Combine {i}"):
+                fd = moe.combine_exchange(eo, recv_splits, send_splits)
+            with record_function(f"S{i}: Finalize {i}"):
+                outs[i] = moe.unpermute(fd, rev, w, shape)
+        gated[i] = dispatched[i] = None
+    return outs

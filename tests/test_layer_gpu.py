@@ -140,3 +140,36 @@ def test_config4_full_size_identity_property():
     gerr = float((x.grad.float() - grad_out.float()).abs().max() / grad_out.float().abs().max())
     assert gerr <= 2e-2, gerr
     assert ops.read_status() == 0
+
+
+@pytest.mark.parametrize("impl", [MoEImplementation.FAST, MoEImplementation.STANDARD])
+def test_swiglu_layer_matches_fp32_reference(impl):
+    """SwiGLU experts (the expert-parallel benchmark's FFN): the FAST path runs the tcgen05
+    grouped GEMM, the STANDARD path per-expert matrix products; both against a plain PyTorch
+    fp32 evaluation of the same layer with the same routing."""
+    torch.manual_seed(0)
+    T, D, FF, E, K = 512, 256, 128, 8, 2
+    moe = MoEFeedForward(D, FF, E, K, impl, expert_type="swiglu").to(DEV).bfloat16()
+    with torch.no_grad():
+        for prm in moe.parameters():
+            prm.normal_(0, 0.05)
+    x = torch.randn(1, T, D, device=DEV).bfloat16().requires_grad_(True)
+    out = moe(x)
+    out.float().pow(2).sum().backward()
+    assert ops.read_status() == 0
+    # fp32 reference with the layer's own routing decision
+    xf = x.detach().float().view(T, D)
+    logits = moe.router(x.detach().view(T, D))
+    w, idx = routing.route_topk(logits, K, w_dtype=torch.bfloat16)
+    ref = torch.zeros(T, D, device=DEV)
+    wgu, wd = moe.experts.w_gate_up.detach().float(), moe.experts.w_down.detach().float()
+    for k in range(K):
+        for e in range(E):
+            m = idx[:, k] == e
+            h = xf[m] @ wgu[e].t()
+            a = (torch.nn.functional.silu(h[:, :FF]) * h[:, FF:]).bfloat16().float()  # hidden is stored in bf16
+            ref[m] += (a @ wd[e].t()).bfloat16().float() * w[m, k].float()[:, None]
+    err = float((out.float().view(T, D) - ref).abs().max() / ref.abs().max())
+    assert err <= 2e-2, err
+    assert x.grad is not None and moe.experts.w_gate_up.grad is not None and moe.router.weight.grad is not None
+    assert torch.isfinite(x.grad.float()).all()
