@@ -66,6 +66,16 @@ NCU_TRAFFIC_BYTES = {DEFAULT_WORKLOAD: 4 * (537_091_584 + 45_902_592)}
 FALLBACK_HBM_GBS = 6650.0
 
 
+def measured_tflops():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["bf16_tflops_sustained"]), "measured (sustained)"
+        except Exception:
+            pass
+    return 1400.0, "fallback"
+
+
 def measured_peak():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -299,6 +309,16 @@ def run_ours(args, rank, world, local_rank):
     value = nbytes * world * args.steps / (elapsed_ms / 1e3) / 1e9
     e2e_value = nbytes * world * e2e_steps / e2e_s / 1e9
 
+    # second part of the headline metric: the expert-parallel MoE layer at this world size
+    ep = None
+    if args.workload == DEFAULT_WORKLOAD and not args.no_ep:
+        n_rows = wl.N
+        del wl, out, arena
+        torch.cuda.empty_cache()
+        ep = ep_layer_bench(rank, world, local_rank, min(args.steps, 20), min(args.warmup, 5))
+    else:
+        n_rows = wl.N
+
     if rank != 0:
         return
 
@@ -349,7 +369,7 @@ def run_ours(args, rank, world, local_rank):
         "data": "synthetic",
         "config": {
             "workload": args.workload, "T": T, "D": D, "E": E, "top_k": K, "routing": routing,
-            "rows": wl.N, "l2": "inputs (2.15 GB) exceed the 126 MB L2; no flush needed",
+            "rows": n_rows, "l2": "inputs (2.15 GB) exceed the 126 MB L2; no flush needed",
             "multi_gpu": "replicas only",
         },
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -358,6 +378,112 @@ def run_ours(args, rank, world, local_rank):
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
         "clocks": clocks.summary(),
+        "ep_layer": ep,
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+EP_WORKLOAD = "ep_moe_layer_cfg5_bf16_8192tok_D7168_E256_top8_swiglu2048"
+
+
+def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
+    """Expert-parallel MoE layer forward: 8192 tokens per rank, D=7168, 256 experts sharded
+    evenly over the ranks, top-8 softmax router, SwiGLU experts 7168->2048->7168, weights
+    N(0, 0.02). Micro-batches: max(1, world/2) (4 at 8 ranks) on as many streams, the exchange of one
+    overlapping the experts of another. Every micro-batch streams the rank's expert weights
+    from HBM once more (22.5 GB / world each time) and thins the rows per expert, so with
+    few ranks fewer micro-batches are faster (measured at 2 ranks: one 9.5 ms, two 11.3 ms);
+    a single rank has no exchange to hide. Returns tokens/s over all ranks (max time over ranks)."""
+    import torch
+    import torch.distributed as dist
+
+    from fastmoe_b200.consts import MoEImplementation
+    from fastmoe_b200.models.tiny_model import MoEFeedForward, pipelined_moe_forward
+
+    dev = torch.device("cuda", local_rank)
+    T, D, FF, E, K = 8192, 7168, 2048, 256, 8
+    MB = micro_batches or max(1, world // 2)  # keeps >= 512 rows per expert and micro-batch on average
+    with torch.device(dev):
+        moe = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST, expert_type="swiglu")
+    moe = moe.to(torch.bfloat16)
+    e_local = moe.num_local_experts
+    gen = torch.Generator(device=dev)
+    with torch.no_grad():
+        gen.manual_seed(0)
+        moe.router.weight.normal_(0, 0.02, generator=gen)
+        for e in range(e_local):  # seeded by the GLOBAL expert id: the same experts at every world size
+            gen.manual_seed(1000 + rank * e_local + e)
+            moe.experts.w_gate_up[e].normal_(0, 0.02, generator=gen)
+            moe.experts.w_down[e].normal_(0, 0.02, generator=gen)
+        gen.manual_seed(100 + rank)
+        x = torch.randn(T, D, generator=gen, device=dev, dtype=torch.bfloat16)
+    chunks = [c.view(1, T // MB, D) for c in x.chunk(MB, 0)]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(MB)]
+    main = torch.cuda.current_stream()
+
+    def step():
+        for s in streams:
+            s.wait_stream(main)
+        with torch.no_grad():
+            outs = pipelined_moe_forward(moe, chunks, streams)
+        for s in streams:
+            main.wait_stream(s)
+        return outs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(warmup, 3)):
+        outs = step()
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        outs = step()
+    end.record()
+    barrier()
+    ms = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms[0]) / steps
+    assert all(bool(torch.isfinite(o.float()).all()) for o in outs)
+    gemm_flops = 6 * T * K * D * FF  # per rank and step: three D x FF products per routed row
+    a2a_bytes = T * K * D * 2 * (world - 1) / world  # leaving each GPU, per direction
+    del moe
+    torch.cuda.empty_cache()
+    return {
+        "tokens_per_s": T * world / (ms / 1e3),
+        "ms_per_step": ms,
+        "tokens_per_rank": T, "micro_batches": MB, "pass": "forward",
+        "gemm_tflops_per_gpu": gemm_flops / (ms / 1e3) / 1e12,
+        "gemm_flops_per_rank": gemm_flops,
+        "a2a_bytes_out_per_rank_per_direction": a2a_bytes,
+        "experts_per_rank": e_local,
+        "config": {"D": D, "ff": FF, "E": E, "top_k": K, "experts": "swiglu", "weights": "N(0,0.02) seeded per expert"},
+    }  # fmt: skip
+
+
+def run_ep(args, rank, world, local_rank):
+    import torch
+
+    torch.cuda.set_device(local_rank)
+    r = ep_layer_bench(rank, world, local_rank, args.steps, args.warmup, args.micro_batches)
+    if rank != 0:
+        return
+    peak, kind = measured_tflops()
+    line = {
+        "metric": "ep_moe_layer_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": EP_WORKLOAD, **r["config"], "tokens_per_rank": r["tokens_per_rank"],
+                   "micro_batches": r["micro_batches"], "parallelism": f"ep{world}", "pass": "forward"},
+        "e2e": None, "gpu_launches": None,
+        "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (share of the whole layer step)",
+                     "achieved": r["gemm_tflops_per_gpu"], "peak": peak, "peak_kind": kind, "unit": "TFLOP/s",
+                     "frac": r["gemm_tflops_per_gpu"] / peak, "traffic": None},
+        "ep_layer": r,
     }  # fmt: skip
     print(json.dumps(line), flush=True)
 
@@ -454,7 +580,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(CFG4), default=DEFAULT_WORKLOAD)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(CFG4) + [EP_WORKLOAD], default=DEFAULT_WORKLOAD)
+    ap.add_argument("--micro-batches", type=int, default=None, help="expert-parallel layer: micro-batches per step")
+    ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel layer part of the default run")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -474,6 +602,8 @@ def main():
     try:
         if args.workload in CFG4:
             run_cfg4(args, rank, world, local_rank)
+        elif args.workload == EP_WORKLOAD:
+            run_ep(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:

@@ -77,30 +77,39 @@ def exchange_counts(send_expert_counts: torch.Tensor, send_rank_counts: torch.Te
     return recv_counts, nested, send_list, recv_list
 
 
-def regroup_indices(counts_by_source, device):
+def regroup_indices(counts_by_source, device, host_counts=None):
     """Row permutations between the arrival order (source rank, then local expert) and the
     order the expert FFN wants (local expert, then source rank).
 
-    counts_by_source[s][e] rows came from rank s for local expert e. Returns
-    (to_expert_major, to_rank_major, tokens_per_local_expert).
+    counts_by_source: [world, E_local] counts (nested lists or a tensor); counts_by_source[s][e]
+    rows came from rank s for local expert e. Returns (to_expert_major, to_rank_major,
+    tokens_per_local_expert as a list). A handful of vectorised tensor operations on
+    `device`, independent of world * E_local in launch count. Pass the counts as a device
+    tensor together with `host_counts` (the same numbers as nested lists) to avoid both a
+    host-to-device copy and a read-back.
     """
-    world = len(counts_by_source)
-    e_local = len(counts_by_source[0]) if world else 0
-    starts, run = [[0] * e_local for _ in range(world)], 0
-    for s in range(world):
-        for e in range(e_local):
-            starts[s][e] = run
-            run += counts_by_source[s][e]
-    pieces, tokens_per_expert = [], []
-    for e in range(e_local):
-        total = 0
-        for s in range(world):
-            n = counts_by_source[s][e]
-            if n:
-                pieces.append(torch.arange(starts[s][e], starts[s][e] + n))
-            total += n
-        tokens_per_expert.append(total)
-    to_expert_major = torch.cat(pieces) if pieces else torch.zeros(0, dtype=torch.int64)
+    if host_counts is not None:  # the caller already holds the counts on the host: no read-back
+        host = host_counts
+    else:
+        host = counts_by_source.tolist() if torch.is_tensor(counts_by_source) else counts_by_source
+    world = len(host)
+    e_local = len(host[0]) if world else 0
+    tokens_per_expert = [sum(host[s][e] for s in range(world)) for e in range(e_local)]
+    total = sum(tokens_per_expert)
+    if torch.is_tensor(counts_by_source):
+        counts = counts_by_source.to(device=device, dtype=torch.int64)
+    else:
+        counts = torch.tensor(host, dtype=torch.int64).reshape(world, e_local).to(device)
+    if total == 0:
+        empty = torch.zeros(0, dtype=torch.int64, device=device)
+        return empty, empty.clone(), tokens_per_expert
+    flat_rm = counts.reshape(-1)  # segments in arrival order (s, e)
+    rm_start = torch.cumsum(flat_rm, 0) - flat_rm
+    counts_em = counts.t().reshape(-1)  # segments in expert-major order (e, s)
+    em_start = torch.cumsum(counts_em, 0) - counts_em
+    rm_start_em = rm_start.reshape(world, e_local).t().reshape(-1)  # arrival start of each (e, s) segment
+    seg = torch.repeat_interleave(torch.arange(counts_em.numel(), device=device), counts_em, output_size=total)
+    to_expert_major = rm_start_em[seg] + (torch.arange(total, device=device) - em_start[seg])
     to_rank_major = torch.empty_like(to_expert_major)
-    to_rank_major[to_expert_major] = torch.arange(to_expert_major.numel())
-    return to_expert_major.to(device), to_rank_major.to(device), tokens_per_expert
+    to_rank_major[to_expert_major] = torch.arange(total, device=device)
+    return to_expert_major, to_rank_major, tokens_per_expert

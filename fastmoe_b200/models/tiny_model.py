@@ -141,14 +141,19 @@ class MoEFeedForward(nn.Module):
             counts.device_counts = device_counts
             total = [sum(counts)]
             return permuted_data, total, list(total), counts
-        _, nested, send_list, recv_list = exchange.exchange_counts(send_expert_counts, send_rank_counts, self.group)
+        recv_counts, nested, send_list, recv_list = exchange.exchange_counts(
+            send_expert_counts, send_rank_counts, self.group
+        )
         recv = exchange.all_to_all_rows(permuted_data, recv_list, send_list, self.group)
-        to_expert_major, to_rank_major, tokens_per_expert = exchange.regroup_indices(nested, recv.device)
         splits = exchange.SplitList(recv_list)
-        splits.to_expert_major, splits.to_rank_major, splits.counts_by_source = to_expert_major, to_rank_major, nested
+        splits.counts_by_source = nested
+        tokens_per_expert = exchange.SplitList(sum(nested[s][e] for s in range(self.world_size))
+                                               for e in range(self.num_local_experts))  # fmt: skip
+        tokens_per_expert.device_counts = recv_counts.sum(dim=0)
         if self.num_local_experts > 1:
+            to_expert_major, to_rank_major, _ = exchange.regroup_indices(recv_counts, recv.device, nested)
+            splits.to_expert_major, splits.to_rank_major = to_expert_major, to_rank_major
             recv = recv.index_select(0, to_expert_major)
-        tokens_per_expert = exchange.SplitList(tokens_per_expert)
         return recv, splits, send_list, tokens_per_expert
 
     # -- stage 3 ---------------------------------------------------------------------------

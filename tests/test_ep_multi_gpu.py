@@ -1,0 +1,116 @@
+"""Expert-parallel MoE layer on 2 GPUs over NCCL against the single-rank computation over all
+experts (the ground truth: the reference's own multi-rank path is wrong for more than one
+expert per rank and carries no gradients). Skipped on boxes with fewer than 2 GPUs."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _expert_weights(e, D, FF, device):
+    g = torch.Generator(device=device).manual_seed(500 + e)
+    wgu = torch.empty(2 * FF, D, device=device).normal_(0, 0.05, generator=g).bfloat16()
+    wd = torch.empty(D, FF, device=device).normal_(0, 0.05, generator=g).bfloat16()
+    return wgu, wd
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from fastmoe_b200.consts import MoEImplementation
+        from fastmoe_b200.kernels import ops, routing
+        from fastmoe_b200.models.tiny_model import MoEFeedForward, pipelined_moe_forward
+
+        T, D, FF, E, K = 384, 256, 128, 8, 2
+        moe = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST, expert_type="swiglu").to(dev).bfloat16()
+        assert moe.world_size == world and moe.num_local_experts == E // world
+        g = torch.Generator(device=dev).manual_seed(7)
+        with torch.no_grad():
+            moe.router.weight.copy_(torch.empty(E, D, device=dev).normal_(0, 0.3, generator=g))
+            for e in range(moe.num_local_experts):
+                wgu, wd = _expert_weights(rank * moe.num_local_experts + e, D, FF, dev)
+                moe.experts.w_gate_up[e].copy_(wgu)
+                moe.experts.w_down[e].copy_(wd)
+        gx = torch.Generator(device=dev).manual_seed(100 + rank)
+        x = torch.randn(1, T, D, generator=gx, device=dev).bfloat16().requires_grad_(True)
+        out = moe(x)
+        coeff = torch.randn(1, T, D, generator=gx, device=dev)
+        (out.float() * coeff).sum().backward()
+        assert ops.read_status() == 0
+
+        # ground truth on this rank's tokens with ALL experts, fp32 math on the same bf16 values
+        xf = x.detach().float().view(T, D).requires_grad_(True)
+        logits = moe.router(x.detach().view(T, D))
+        _, idx = routing.route_topk(logits, K, w_dtype=torch.bfloat16)  # the layer's routing decision
+        # gate weights recomputed in fp32 with autograd, so the router path carries gradient too
+        w = torch.softmax(torch.gather(xf @ moe.router.weight.detach().float().t(), 1, idx), dim=-1)
+        ref = torch.zeros(T, D, device=dev)
+        for e in range(E):
+            wgu, wd = _expert_weights(e, D, FF, dev)
+            for k in range(K):
+                m = idx[:, k] == e
+                h = xf[m] @ wgu.float().t()
+                a = torch.nn.functional.silu(h[:, :FF]) * h[:, FF:]
+                ref = ref.index_add(0, m.nonzero().view(-1), (a @ wd.float().t()) * w[m, k].float()[:, None])
+        (ref * coeff.view(T, D)).sum().backward()
+        err = float((out.float().view(T, D) - ref).abs().max() / ref.abs().max())
+        assert err <= 2e-2, f"forward rel err {err}"
+        # gradient w.r.t. the tokens: through experts living on both ranks and through the router
+        gerr = float((x.grad.float().view(T, D) - xf.grad).abs().max() / xf.grad.abs().max())
+        assert gerr <= 5e-2, f"grad rel err {gerr}"
+        assert moe.experts.w_down.grad is not None and float(moe.experts.w_down.grad.abs().max()) > 0
+
+        # the pipelined schedule gives the same result as the plain forward
+        chunks = [c.contiguous() for c in x.detach().view(4, T // 4, D).unsqueeze(1)]
+        streams = [torch.cuda.Stream(device=dev) for _ in chunks]
+        for s in streams:
+            s.wait_stream(torch.cuda.current_stream())
+        with torch.no_grad():
+            outs = pipelined_moe_forward(moe, chunks, streams)
+        torch.cuda.synchronize()
+        piped = torch.cat(outs, 1).view(T, D)
+        perr = float((piped.float() - ref.detach()).abs().max() / ref.abs().max())
+        assert perr <= 2e-2, f"pipelined rel err {perr}"
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:
+        import traceback
+
+        q.put(f"rank {rank}: {exc}\n{traceback.format_exc()}")
+        raise
+
+
+def test_ep_layer_two_gpus_matches_single_rank_ground_truth():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    msgs = []
+    while not q.empty():
+        msgs.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert not msgs, "\n".join(msgs)
+    assert all(p.exitcode == 0 for p in procs)
