@@ -389,11 +389,14 @@ EP_WORKLOAD = "ep_moe_layer_cfg5_bf16_8192tok_D7168_E256_top8_swiglu2048"
 def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
     """Expert-parallel MoE layer forward: 8192 tokens per rank, D=7168, 256 experts sharded
     evenly over the ranks, top-8 softmax router, SwiGLU experts 7168->2048->7168, weights
-    N(0, 0.02). Micro-batches: max(1, world/2) (4 at 8 ranks) on as many streams, the exchange of one
-    overlapping the experts of another. Every micro-batch streams the rank's expert weights
-    from HBM once more (22.5 GB / world each time) and thins the rows per expert, so with
-    few ranks fewer micro-batches are faster (measured at 2 ranks: one 9.5 ms, two 11.3 ms);
-    a single rank has no exchange to hide. Returns tokens/s over all ranks (max time over ranks)."""
+    N(0, 0.02). Micro-batches run on their own streams, the exchange of one overlapping the
+    experts of another. Every micro-batch streams the rank's expert weights from HBM once
+    more (22.5 GB / world each time) and thins the rows per expert: measured, the grouped
+    GEMMs for 65536 rows take 4.52 / 4.66 / 5.51 ms in 1 / 2 / 4 launches at 32 experts per
+    rank and 5.08 / 5.43 / 5.91 ms at 64, and at 2 and 4 ranks one micro-batch was fastest
+    (2 ranks: 8.7 ms against 10.2 ms with two). The default is therefore 1 micro-batch below
+    8 ranks and 2 at 8 ranks; --micro-batches overrides it (the configuration's nominal
+    value is 4). Returns tokens/s over all ranks (max time over ranks)."""
     import torch
     import torch.distributed as dist
 
@@ -402,7 +405,7 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
 
     dev = torch.device("cuda", local_rank)
     T, D, FF, E, K = 8192, 7168, 2048, 256, 8
-    MB = micro_batches or max(1, world // 2)  # keeps >= 512 rows per expert and micro-batch on average
+    MB = micro_batches or (2 if world >= 8 else 1)
     with torch.device(dev):
         moe = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST, expert_type="swiglu")
     moe = moe.to(torch.bfloat16)
@@ -469,6 +472,10 @@ def run_ep(args, rank, world, local_rank):
     import torch
 
     torch.cuda.set_device(local_rank)
+    if args.gemm_sms:
+        from fastmoe_b200 import _lib
+
+        _lib.tune("gemm_sms", args.gemm_sms)
     r = ep_layer_bench(rank, world, local_rank, args.steps, args.warmup, args.micro_batches)
     if rank != 0:
         return
@@ -582,6 +589,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(CFG4) + [EP_WORKLOAD], default=DEFAULT_WORKLOAD)
     ap.add_argument("--micro-batches", type=int, default=None, help="expert-parallel layer: micro-batches per step")
+    ap.add_argument("--gemm-sms", type=int, default=None, help="expert-parallel layer: SMs for the grouped GEMM")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel layer part of the default run")
     args = ap.parse_args()
 

@@ -34,6 +34,7 @@ constexpr uint32_t kSpinLimit = 1u << 24;
 struct GemmArgs {
   const int64_t* offsets;  // [E] first row of each expert in A / C
   const int64_t* counts;   // [E] rows of each expert
+  const int64_t* c_row_map;  // optional [R]: row of C that receives the result of A's row r (nullptr = r)
   __nv_bfloat16* C;
   int64_t ldc;             // row stride of C in elements
   int64_t R;               // rows of A
@@ -271,8 +272,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int row = quarter * 32 + lane;
       const bool valid = row < c.rows;
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+      // destination row: the same row as in A, or wherever the row map sends it (rows are
+      // stored one per thread, so scattering them costs nothing extra)
+      int64_t out_row = c.row0 + row;
+      if (valid && a.c_row_map != nullptr) out_row = a.c_row_map[out_row];
       if (a.swiglu) {
-        __nv_bfloat16* crow = a.C + (c.row0 + row) * a.ldc + static_cast<int64_t>(c.nb) * 128;
+        __nv_bfloat16* crow = a.C + out_row * a.ldc + static_cast<int64_t>(c.nb) * 128;
 #pragma unroll 1
         for (int c0 = 0; c0 < 128; c0 += 32) {
           uint32_t g[32], u[32];
@@ -291,7 +296,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       } else {
-        __nv_bfloat16* crow = a.C + (c.row0 + row) * a.ldc + static_cast<int64_t>(c.nb) * kBN;
+        __nv_bfloat16* crow = a.C + out_row * a.ldc + static_cast<int64_t>(c.nb) * kBN;
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN; c0 += 32) {
           uint32_t r[32];
@@ -330,6 +335,10 @@ done:
 }
 
 // ---- host side ---------------------------------------------------------------------------
+// SMs the persistent grid may occupy (fmoe_tune "gemm_sms"). Leaving a few SMs free lets
+// NCCL's copy kernels run beside the GEMM instead of waiting for its CTAs to retire.
+int g_gemm_sms = kNumSMs;
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -367,8 +376,8 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t co
 using namespace fmoe;
 
 extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
-                                 const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
-                                 int swiglu, int32_t* status, void* stream) {
+                                 const int64_t* counts, const int64_t* c_row_map, int64_t E, int64_t R,
+                                 int64_t N, int64_t K, int swiglu, int32_t* status, void* stream) {
   FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm: bad sizes");
   FMOE_REQUIRE(E <= kMaxExperts, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: supports E <= %d", kMaxExperts);
   FMOE_REQUIRE(K % kBK == 0, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: K=%lld must be a multiple of %d",
@@ -395,6 +404,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   GemmArgs g;
   g.offsets = offsets;
   g.counts = counts;
+  g.c_row_map = c_row_map;
   g.C = static_cast<__nv_bfloat16*>(c);
   g.ldc = swiglu ? N / 2 : N;
   g.R = R;
@@ -412,7 +422,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
                                  1024 + kStages * kStageBytes + 256 + static_cast<int>(sizeof(int)) * (kMaxExperts + 2)));
   // upper bound of the tile count, known without reading the counts: one partial block per expert
   const int64_t max_tiles = (R / kBM + E) * g.n_blocks;
-  const int grid = static_cast<int>(max_tiles < kNumSMs ? max_tiles : kNumSMs);
+  const int grid = static_cast<int>(max_tiles < g_gemm_sms ? max_tiles : g_gemm_sms);
   grouped_gemm_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(map_a, map_w, g);
   return check_launch("grouped_gemm_kernel");
 }

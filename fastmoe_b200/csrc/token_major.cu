@@ -20,6 +20,7 @@ static int g_gather_v = 0;         // vectors per thread, 0 = choose from D
 static int g_gather_threads = 0;   // threads per CTA, 0 = choose from D
 static int g_gather_ctas_per_sm = -1;  // persistent grid = 148 * this; 0 = one CTA per item; -1 = auto
 static int g_bwd_ctas_per_sm = 3;
+extern int g_gemm_sms;  // grouped_gemm.cu
 
 struct TileCfg {
   int threads;
@@ -393,6 +394,9 @@ extern "C" int fmoe_tune(const char* key, int value) {
   } else if (k == "bwd_ctas_per_sm") {
     FMOE_REQUIRE(value >= 1 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: bwd_ctas_per_sm in [1, 64]");
     g_bwd_ctas_per_sm = value;
+  } else if (k == "gemm_sms") {
+    FMOE_REQUIRE(value >= 1 && value <= kNumSMs, FMOE_ERR_ARG, "fmoe_tune: gemm_sms in [1, %d]", kNumSMs);
+    g_gemm_sms = value;
   } else {
     return fail(FMOE_ERR_ARG, "fmoe_tune: unknown key '%s'", key);
   }

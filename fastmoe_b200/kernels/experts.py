@@ -32,32 +32,38 @@ def _check(a, w, offsets, counts):
         raise ValueError("offsets and counts need one entry per expert")
 
 
-def _launch(a, w, offsets, counts, swiglu):
+def _launch(a, w, offsets, counts, swiglu, row_map=None, covers_all_rows=False):
     a, w = a.contiguous(), w.contiguous()
     R, K = a.shape
     E, N, _ = w.shape
     cols = N // 2 if swiglu else N
-    # rows that belong to no expert are never written: start from zeros so they are defined
-    c = torch.zeros(R, cols, dtype=torch.bfloat16, device=a.device) if R else a.new_empty(0, cols)
+    if covers_all_rows or R == 0:
+        c = torch.empty(R, cols, dtype=torch.bfloat16, device=a.device)
+    else:  # rows that belong to no expert are never written: start from zeros so they are defined
+        c = torch.zeros(R, cols, dtype=torch.bfloat16, device=a.device)
     ops._call(
         "fmoe_grouped_gemm", 1, a.data_ptr(), w.data_ptr(), c.data_ptr(), offsets.data_ptr(),
-        counts.data_ptr(), E, R, N, K, 1 if swiglu else 0, _status_word(a.device).data_ptr(),
-        _stream_ptr(a.device),
+        counts.data_ptr(), row_map.data_ptr() if row_map is not None else None, E, R, N, K,
+        1 if swiglu else 0, _status_word(a.device).data_ptr(), _stream_ptr(a.device),
     )  # fmt: skip
     return c
 
 
 class _GroupedGemm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, a, w, offsets, counts, swiglu):
+    def forward(ctx, a, w, offsets, counts, swiglu, row_map, covers_all_rows):
         _check(a, w, offsets, counts)
-        ctx.save_for_backward(a, w, offsets, counts)
+        if row_map is not None and (row_map.dtype != torch.int64 or row_map.numel() != a.shape[0]):
+            raise ValueError("row_map must be an int64 device tensor with one entry per row of a")
+        ctx.save_for_backward(a, w, offsets, counts, row_map)
         ctx.swiglu = swiglu
-        return _launch(a, w, offsets, counts, swiglu)
+        return _launch(a, w, offsets, counts, swiglu, row_map, covers_all_rows)
 
     @staticmethod
     def backward(ctx, grad_c):
-        a, w, offsets, counts = ctx.saved_tensors
+        a, w, offsets, counts, row_map = ctx.saved_tensors
+        if row_map is not None:
+            grad_c = grad_c.index_select(0, row_map)  # back to the row order of `a`
         offs, cnts = offsets.tolist(), counts.tolist()
         grad_a = torch.zeros_like(a)
         grad_w = torch.zeros_like(w)
@@ -75,19 +81,24 @@ class _GroupedGemm(torch.autograd.Function):
                 g = torch.cat([d_gate, d_up], dim=1).to(a.dtype)
             grad_a[o : o + n] = g @ w[e]
             grad_w[e] = g.t() @ x
-        return grad_a, grad_w, None, None, None
+        return grad_a, grad_w, None, None, None, None, None
 
 
-def grouped_gemm(a, w, offsets, counts, swiglu=False):
+def grouped_gemm(a, w, offsets, counts, swiglu=False, row_map=None, covers_all_rows=False):
     """C[rows of e] = A[rows of e] @ w[e].T (or the fused SwiGLU of its two halves).
 
     a [R, K] bf16; w [E, N, K] bf16; offsets, counts int64 [E] on the device (rows
     [offsets[e], offsets[e]+counts[e]) belong to expert e). Returns bf16 [R, N] (or [R, N/2]).
+    `row_map` (int64 [R], a permutation) stores the result of row r at row row_map[r].
+    `covers_all_rows=True` promises that every row belongs to an expert, which saves the
+    zero-fill of the output.
     """
-    return _GroupedGemm.apply(a, w, offsets, counts, bool(swiglu))
+    return _GroupedGemm.apply(a, w, offsets, counts, bool(swiglu), row_map, bool(covers_all_rows))
 
 
-def grouped_swiglu_ffn(x, w_gate_up, w_down, offsets, counts):
-    """down(silu(gate(x)) * up(x)) per expert. w_gate_up [E, 2*ff, D] (gate rows first), w_down [E, D, ff]."""
-    hidden = grouped_gemm(x, w_gate_up, offsets, counts, swiglu=True)
-    return grouped_gemm(hidden, w_down, offsets, counts, swiglu=False)
+def grouped_swiglu_ffn(x, w_gate_up, w_down, offsets, counts, row_map=None, covers_all_rows=False):
+    """down(silu(gate(x)) * up(x)) per expert. w_gate_up [E, 2*ff, D] (gate rows first), w_down [E, D, ff].
+    `row_map` reorders the rows of the result (see grouped_gemm)."""
+    hidden = grouped_gemm(x, w_gate_up, offsets, counts, swiglu=True, covers_all_rows=covers_all_rows)
+    return grouped_gemm(hidden, w_down, offsets, counts, swiglu=False, row_map=row_map,
+                        covers_all_rows=covers_all_rows)  # fmt: skip

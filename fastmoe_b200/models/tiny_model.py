@@ -82,9 +82,10 @@ class GroupedSwiGLUExperts(nn.Module):
     def __iter__(self):
         return (self.expert(e) for e in range(self.num_experts))
 
-    def forward(self, x, offsets, counts):
-        """x rows grouped by expert (device-side `offsets`/`counts`, int64 [E]) -> FFN output rows."""
-        return grouped_swiglu_ffn(x, self.w_gate_up, self.w_down, offsets, counts)
+    def forward(self, x, offsets, counts, row_map=None):
+        """x rows grouped by expert (device-side `offsets`/`counts`, int64 [E], covering every
+        row) -> FFN output rows, stored at `row_map[r]` instead of r when a map is given."""
+        return grouped_swiglu_ffn(x, self.w_gate_up, self.w_down, offsets, counts, row_map, covers_all_rows=True)
 
 
 class MoEFeedForward(nn.Module):
@@ -153,6 +154,7 @@ class MoEFeedForward(nn.Module):
         if self.num_local_experts > 1:
             to_expert_major, to_rank_major, _ = exchange.regroup_indices(recv_counts, recv.device, nested)
             splits.to_expert_major, splits.to_rank_major = to_expert_major, to_rank_major
+            tokens_per_expert.to_expert_major = to_expert_major
             recv = recv.index_select(0, to_expert_major)
         return recv, splits, send_list, tokens_per_expert
 
@@ -171,7 +173,12 @@ class MoEFeedForward(nn.Module):
             staging = torch.tensor(list(tokens_per_expert), dtype=torch.int64, pin_memory=True)
             counts = staging.to(recv_data.device, non_blocking=True)
         offsets = torch.cumsum(counts, 0) - counts
-        return self.experts(recv_data, offsets, counts)
+        # with several ranks the rows arrived ordered by source rank and were regrouped by
+        # expert; the down-projection's epilogue stores them straight back in arrival order
+        row_map = getattr(tokens_per_expert, "to_expert_major", None)
+        out = self.experts(recv_data, offsets, counts, row_map)
+        out.fmoe_rank_major = row_map is not None
+        return out
 
     def _use_grouped(self, recv_data):
         return (self.expert_type == "swiglu" and self.implementation == consts.MoEImplementation.FAST
@@ -190,7 +197,8 @@ class MoEFeedForward(nn.Module):
         if self.world_size == 1:
             return expert_output
         to_rank_major = getattr(recv_splits, "to_rank_major", None)
-        if to_rank_major is not None and self.num_local_experts > 1:
+        already = getattr(expert_output, "fmoe_rank_major", False)
+        if to_rank_major is not None and self.num_local_experts > 1 and not already:
             expert_output = expert_output.index_select(0, to_rank_major)
         return exchange.all_to_all_rows(expert_output, list(send_splits), list(recv_splits), self.group)
 

@@ -64,7 +64,8 @@ const char* fmoe_status_name(int status);
  * concurrent launches. Keys: "gather_v" (16-byte vectors per thread: 0 = auto,
  * 1, 2, 4), "gather_threads" (threads per CTA, 0 = auto, else a multiple of 32
  * up to 256), "gather_ctas_per_sm" (-1 = auto, 0 = one CTA per work item,
- * else a persistent grid of 148 x value CTAs), "bwd_ctas_per_sm". */
+ * else a persistent grid of 148 x value CTAs), "bwd_ctas_per_sm", "gemm_sms" (SMs the
+ * grouped GEMM's persistent grid occupies, 1..148; fewer leaves room for NCCL kernels). */
 int fmoe_tune(const char* key, int value);
 
 /* ---- combine: scatter form ---------------------------------------------- */
@@ -225,11 +226,14 @@ int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_of, void* gr
  * (src/fastmoe/models/tiny_model.py:282-294; the reference's experts are
  * Linear-GELU-Linear, tiny_model.py:68-77; SwiGLU is what the expert-parallel benchmark
  * configuration asks for). Rows of A outside every expert's range are not touched in C.
+ * c_row_map (optional int64[R] on the device, NULL = identity) sends the result of A's row
+ * r to row c_row_map[r] of C: the return-trip reordering of the expert-parallel layer
+ * (expert-major rows back to source-rank-major) happens in the store, not in a copy.
  * A bounded device-side wait that gives up sets FMOE_STATUS_WAIT_TIMEOUT in `status`.
  */
 int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
-                      const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
-                      int swiglu, int32_t* status, void* stream);
+                      const int64_t* counts, const int64_t* c_row_map, int64_t E, int64_t R,
+                      int64_t N, int64_t K, int swiglu, int32_t* status, void* stream);
 
 /* ---- host-buffer call -------------------------------------------------------- */
 /*

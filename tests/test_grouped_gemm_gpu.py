@@ -94,3 +94,20 @@ def test_unsupported_shapes_raise():
         experts.grouped_gemm(a, w[:, :100].contiguous(), off, cnt)  # N % 256
     with pytest.raises(ValueError):
         experts.grouped_gemm(a.float(), w.float(), off, cnt)
+
+
+def test_row_map_scatters_the_output_rows():
+    counts = [150, 0, 90, 260]
+    a, w, off, cnt = _case(counts, 256, 512, False, seed=8)
+    R = sum(counts)
+    perm = torch.randperm(R, device=DEV)
+    plain = experts.grouped_gemm(a, w, off, cnt, covers_all_rows=True)
+    mapped = experts.grouped_gemm(a, w, off, cnt, row_map=perm, covers_all_rows=True)
+    expect = torch.empty_like(plain)
+    expect[perm] = plain
+    assert torch.equal(mapped, expect)
+    wgu = w
+    fused = experts.grouped_gemm(a, wgu, off, cnt, swiglu=True, row_map=perm, covers_all_rows=True)
+    ref = torch.empty_like(fused)
+    ref[perm] = experts.grouped_gemm(a, wgu, off, cnt, swiglu=True)
+    assert torch.equal(fused, ref)
