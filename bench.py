@@ -56,7 +56,17 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "combine_cfg2_bf16_T8192_D16384_E256_top8"
 # dispatch permute + combine, forward and backward under autograd: (T, D, E, K)
-CFG4 = {"dispatch_combine_cfg4_bf16_T16384_D7168_E256_top8": (16384, 7168, 256, 8)}
+CFG4 = {
+    "dispatch_combine_cfg4_bf16_T16384_D7168_E256_top8": (16384, 7168, 256, 8),
+    # a quarter of the tokens: the size used for ncu captures
+    "dispatch_combine_ncu_bf16_T4096_D7168_E256_top8": (4096, 7168, 256, 8),
+}
+# expert FFN alone (two grouped GEMMs, SwiGLU fused): (experts, rows, D, ff)
+GEMM = {
+    "grouped_swiglu_ffn_E32_R65536_D7168_ff2048": (32, 65536, 7168, 2048),  # one rank of 8
+    "grouped_swiglu_ffn_E256_R65536_D7168_ff2048": (256, 65536, 7168, 2048),  # a single rank
+    "grouped_swiglu_ffn_ncu_E8_R8192_D7168_ff2048": (8, 8192, 7168, 2048),  # small case for ncu
+}
 
 # DRAM bytes (read + write) of one gather launch on the default workload: the ncu
 # capture of the quarter-size case (profiles/combine_gather_cfg2.md) scaled by its
@@ -495,6 +505,67 @@ def run_ep(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_gemm(args, rank, world, local_rank):
+    """The expert FFN as two grouped GEMM launches (gate/up with fused SwiGLU, then down)."""
+    import torch
+
+    from fastmoe_b200.kernels import experts, ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    E, R, D, FF = GEMM[args.workload]
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    cnt = torch.full((E,), R // E, dtype=torch.int64, device=dev)
+    jitter = torch.randint(-(R // E // 8), R // E // 8 + 1, (E // 2,), generator=gen, device=dev)
+    cnt[: E // 2] += jitter
+    cnt[E // 2 :] -= jitter  # ragged, same total
+    off = torch.cumsum(cnt, 0) - cnt
+    x = torch.randn(R, D, generator=gen, device=dev, dtype=torch.bfloat16)
+    wgu = torch.empty(E, 2 * FF, D, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+    wd = torch.empty(E, D, FF, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+    flops = 6 * R * D * FF
+
+    def step():
+        with torch.no_grad():
+            return experts.grouped_swiglu_ffn(x, wgu, wd, off, cnt, covers_all_rows=True)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ops.kernel_events = {}
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            y = step()
+        end.record()
+        torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / args.steps
+    pairs = ops.kernel_events.get("fmoe_grouped_gemm", [])
+    ops.kernel_events = None
+    each = [a.elapsed_time(b) for a, b in pairs]
+    gate_up_ms, down_ms = statistics.mean(each[0::2]), statistics.mean(each[1::2])
+    assert ops.read_status(dev) == 0 and bool(torch.isfinite(y.float()).all())
+    if rank != 0:
+        return
+    peak, kind = measured_tflops()
+    achieved = flops / (ms / 1e3) / 1e12
+    line = {
+        "metric": "grouped_swiglu_ffn_tflops", "value": achieved * world, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "experts": E, "rows": R, "D": D, "ff": FF,
+                   "l2": "weights (%.1f GB) exceed the 126 MB L2" % (E * 3 * D * FF * 2 / 1e9)},
+        "e2e": None, "gpu_launches": 2 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (gate/up + down)", "achieved": achieved,
+                     "peak": peak, "peak_kind": kind, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                     "gate_up_ms": gate_up_ms, "gate_up_tflops": 4 * R * D * FF / gate_up_ms / 1e9,
+                     "down_ms": down_ms, "down_tflops": 2 * R * D * FF / down_ms / 1e9},
+        "clocks": clocks.summary(),
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
 def run_cfg4(args, rank, world, local_rank):
     """Index build + dispatch permute + combine, forward and backward, identity experts.
     Reports whole-chain GB/s of algorithmic bytes and a roofline entry per kernel."""
@@ -587,7 +658,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(CFG4) + [EP_WORKLOAD], default=DEFAULT_WORKLOAD)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(CFG4) + sorted(GEMM) + [EP_WORKLOAD], default=DEFAULT_WORKLOAD)
     ap.add_argument("--micro-batches", type=int, default=None, help="expert-parallel layer: micro-batches per step")
     ap.add_argument("--gemm-sms", type=int, default=None, help="expert-parallel layer: SMs for the grouped GEMM")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel layer part of the default run")
@@ -610,6 +681,8 @@ def main():
     try:
         if args.workload in CFG4:
             run_cfg4(args, rank, world, local_rank)
+        elif args.workload in GEMM:
+            run_gemm(args, rank, world, local_rank)
         elif args.workload == EP_WORKLOAD:
             run_ep(args, rank, world, local_rank)
         else:

@@ -106,91 +106,88 @@ __global__ void __launch_bounds__(256)
   if (flags && status != nullptr) atomicOr(status, flags);
 }
 
-// Single CTA of 32 warps. Phase 1: each warp takes experts warp, warp+32, ... and
-// turns that expert's per-chunk counts into an exclusive prefix over the chunks (in
-// place), 32 chunks per step with a shuffle scan. Phase 2: exclusive prefix over the
-// experts' totals (offsets) and the per-rank sums.
-__global__ void __launch_bounds__(1024)
-    index_scan_kernel(int32_t* __restrict__ chunk_hist, int64_t nchunks, int E, int world,
-                      int64_t* __restrict__ counts, int64_t* __restrict__ offsets,
-                      int64_t* __restrict__ rank_counts) {
-  extern __shared__ int32_t totals[];  // [E]
-  __shared__ int64_t warp_sums[32];
-  __shared__ int64_t carry_s;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  if (threadIdx.x == 0) carry_s = 0;
-  if (threadIdx.x < 32) warp_sums[threadIdx.x] = 0;
-  for (int r = threadIdx.x; r < world; r += blockDim.x) rank_counts[r] = 0;
+// One warp per expert: turns that expert's per-chunk counts into an exclusive prefix over
+// the chunks (in place) and leaves the expert's total. Up to 16 x 32 chunks are loaded
+// before the first store, so the strided loads overlap instead of queueing behind stores.
+__global__ void __launch_bounds__(256)
+    index_chunk_scan_kernel(int32_t* __restrict__ chunk_hist, int64_t nchunks, int E,
+                            int32_t* __restrict__ totals) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= E) return;
+  constexpr int kBatch = 16;
+  int32_t carry = 0;
+  for (int64_t base = 0; base < nchunks; base += 32 * kBatch) {
+    int32_t v[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int64_t c = base + 32 * i + lane;
+      v[i] = c < nchunks ? chunk_hist[c * E + e] : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int64_t c = base + 32 * i + lane;
+      int32_t incl = v[i];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int32_t n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+      }
+      if (c < nchunks) chunk_hist[c * E + e] = carry + incl - v[i];
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  if (lane == 0) totals[e] = carry;
+}
 
-  for (int e = warp; e < E; e += nwarps) {
+// Stable placement: slot = offsets[e] + rows of e in earlier chunks + rows of e earlier in
+// this chunk. Every CTA first rebuilds the exclusive prefix over the experts' totals in
+// shared memory (E values: cheaper than another launch); CTA 0 also publishes counts,
+// offsets and the per-rank sums. A warp then walks its chunk in flat order, 32 entries at
+// a time; __match_any_sync ranks equal experts inside a step.
+__global__ void __launch_bounds__(256)
+    index_place_kernel(const int64_t* __restrict__ topk_idx, const void* __restrict__ topk_w,
+                       int w_dtype, int64_t T, int E, int K, int world,
+                       const int32_t* __restrict__ chunk_hist, const int32_t* __restrict__ totals,
+                       int64_t* __restrict__ counts, int64_t* __restrict__ offsets,
+                       int64_t* __restrict__ rank_counts, int64_t* __restrict__ reverse_map,
+                       void* __restrict__ sorted_w, int32_t* __restrict__ slot_of) {
+  extern __shared__ int32_t smem[];
+  int32_t* off_s = smem;          // [E + 1] exclusive prefix of the totals
+  int32_t* cnt_all = smem + E + 1;  // [warps][E] running counts inside each warp's chunk
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+
+  if (warp == 0) {
     int32_t carry = 0;
-#pragma unroll 4
-    for (int64_t base = 0; base < nchunks; base += 32) {
-      const int64_t c = base + lane;
-      const int32_t v = c < nchunks ? chunk_hist[c * E + e] : 0;
+    for (int base = 0; base < E; base += 32) {
+      const int e = base + lane;
+      const int32_t v = e < E ? totals[e] : 0;
       int32_t incl = v;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const int32_t n = __shfl_up_sync(0xffffffffu, incl, d);
         if (lane >= d) incl += n;
       }
-      if (c < nchunks) chunk_hist[c * E + e] = carry + incl - v;
+      if (e < E) off_s[e] = carry + incl - v;
       carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    if (lane == 0) totals[e] = carry;
+    if (lane == 0) off_s[E] = carry;
   }
   __syncthreads();
-
-  const int e_local = E / world;
-  for (int base = 0; base < E; base += blockDim.x) {
-    const int e = base + threadIdx.x;
-    const int64_t total = e < E ? totals[e] : 0;
-    if (e < E) counts[e] = total;
-    int64_t incl = total;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const int64_t n = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += n;
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      counts[e] = off_s[e + 1] - off_s[e];
+      offsets[e] = off_s[e];
     }
-    if (lane == 31) warp_sums[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-      int64_t sum = lane < nwarps ? warp_sums[lane] : 0;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int64_t n = __shfl_up_sync(0xffffffffu, sum, d);
-        if (lane >= d) sum += n;
-      }
-      warp_sums[lane] = sum;
-    }
-    __syncthreads();
-    const int64_t carry = carry_s;
-    if (e < E) {
-      offsets[e] = carry + (warp == 0 ? 0 : warp_sums[warp - 1]) + incl - total;
-      if (total != 0)
-        atomicAdd(reinterpret_cast<unsigned long long*>(&rank_counts[e / e_local]),
-                  static_cast<unsigned long long>(total));
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) carry_s = carry + warp_sums[nwarps - 1];
-    __syncthreads();
+    const int e_local = E / world;
+    for (int r = threadIdx.x; r < world; r += blockDim.x)
+      rank_counts[r] = off_s[(r + 1) * e_local] - off_s[r * e_local];
   }
-}
 
-// Stable placement: slot = offsets[e] + rows of e in earlier chunks + rows of e
-// earlier in this chunk. A warp walks its chunk in flat order, 32 entries at a
-// time; __match_any_sync ranks equal experts inside a step.
-__global__ void __launch_bounds__(256)
-    index_place_kernel(const int64_t* __restrict__ topk_idx, const void* __restrict__ topk_w,
-                       int w_dtype, int64_t T, int E, int K, const int32_t* __restrict__ chunk_hist,
-                       const int64_t* __restrict__ offsets, int64_t* __restrict__ reverse_map,
-                       void* __restrict__ sorted_w, int32_t* __restrict__ slot_of) {
-  extern __shared__ int32_t smem[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int64_t chunk = blockIdx.x * static_cast<int64_t>(nwarps) + warp;
   const int64_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
   if (chunk >= nchunks) return;
-  int32_t* cnt = smem + warp * E;
+  int32_t* cnt = cnt_all + warp * E;
   for (int e = lane; e < E; e += 32) cnt[e] = 0;
   __syncwarp();
   const int64_t first = chunk * kChunkTokens * K;
@@ -210,7 +207,8 @@ __global__ void __launch_bounds__(256)
     if (ok && (peers & lt_mask) == 0) cnt[e] = before + __popc(peers);  // group leader
     __syncwarp();
     if (ok) {
-      const int64_t slot = offsets[e] + chunk_hist[chunk * E + e] + before + __popc(peers & lt_mask);
+      const int64_t slot = static_cast<int64_t>(off_s[e]) + chunk_hist[chunk * E + e] + before +
+                           __popc(peers & lt_mask);
       reverse_map[slot] = i / K;
       store_scalar_from_float(sorted_w, slot, w_dtype, load_scalar_as_float(topk_w, i, w_dtype));
       slot_of[i] = static_cast<int32_t>(slot);
@@ -220,8 +218,17 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Single CTA that publishes all-zero counts, offsets and rank sums when there is nothing to place.
+__global__ void index_empty_kernel(int E, int world, int64_t* counts, int64_t* offsets, int64_t* rank_counts) {
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = offsets[e] = 0;
+  for (int r = threadIdx.x; r < world; r += blockDim.x) rank_counts[r] = 0;
+}
+
+// Warps per CTA of the histogram / placement kernels: per-warp counters of E ints each, plus
+// the E+1 offsets of the placement kernel, inside the default 48 KB of shared memory.
 static int warps_for(int E) {
-  int w = static_cast<int>((48 * 1024) / (sizeof(int32_t) * static_cast<size_t>(E)));
+  int w = static_cast<int>((48 * 1024 - sizeof(int32_t) * (static_cast<size_t>(E) + 1)) /
+                           (sizeof(int32_t) * static_cast<size_t>(E)));
   if (w > 8) w = 8;
   return w;
 }
@@ -264,9 +271,11 @@ extern "C" size_t fmoe_build_index_bytes(int64_t T, int64_t E, int64_t K) {
   (void)K;
   if (T < 0 || E < 0) return 0;
   const int64_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
+  // per-chunk histograms [nchunks][E] followed by the per-expert totals [E]
   return round_up(sizeof(int32_t) * static_cast<size_t>(nchunks > 0 ? nchunks : 1) *
                       static_cast<size_t>(E > 0 ? E : 1),
-                  256);
+                  256) +
+         round_up(sizeof(int32_t) * static_cast<size_t>(E > 0 ? E : 1), 256);
 }
 
 extern "C" int fmoe_build_index(const int64_t* topk_idx, const void* topk_w, int w_dtype, int64_t T,
@@ -279,7 +288,7 @@ extern "C" int fmoe_build_index(const int64_t* topk_idx, const void* topk_w, int
                "fmoe_build_index: sizes must be T >= 0, E > 0, K >= 0, world > 0");
   FMOE_REQUIRE(E % world == 0, FMOE_ERR_ARG, "fmoe_build_index: E=%lld not divisible by world=%lld",
                (long long)E, (long long)world);
-  FMOE_REQUIRE(E <= 8192, FMOE_ERR_UNSUPPORTED, "fmoe_build_index: supports E <= 8192");
+  FMOE_REQUIRE(E <= 4096, FMOE_ERR_UNSUPPORTED, "fmoe_build_index: supports E <= 4096");
   FMOE_REQUIRE(T * K < (1ll << 31), FMOE_ERR_UNSUPPORTED, "fmoe_build_index: T*K must fit in int32");
   FMOE_REQUIRE(counts && offsets && rank_counts, FMOE_ERR_ARG,
                "fmoe_build_index: counts/offsets/rank_counts must not be null");
@@ -291,25 +300,24 @@ extern "C" int fmoe_build_index(const int64_t* topk_idx, const void* topk_w, int
   FMOE_REQUIRE(N == 0 || (topk_idx && topk_w && reverse_map && sorted_w && slot_of), FMOE_ERR_ARG,
                "fmoe_build_index: null pointer argument");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int e = static_cast<int>(E);
+  if (N == 0) {
+    index_empty_kernel<<<1, 256, 0, s>>>(e, static_cast<int>(world), counts, offsets, rank_counts);
+    return check_launch("index_empty_kernel");
+  }
+  const int64_t nchunks = (T + kChunkTokens - 1) / kChunkTokens;
   int32_t* chunk_hist = static_cast<int32_t*>(scratch);
-  const int64_t nchunks = N == 0 ? 0 : (T + kChunkTokens - 1) / kChunkTokens;
-  const int warps = warps_for(static_cast<int>(E));
-  const size_t smem = sizeof(int32_t) * static_cast<size_t>(E) * warps;
+  int32_t* totals = reinterpret_cast<int32_t*>(
+      static_cast<char*>(scratch) + round_up(sizeof(int32_t) * static_cast<size_t>(nchunks) * E, 256));
+  const int warps = warps_for(e);
   const int grid = static_cast<int>((nchunks + warps - 1) / warps);
-  if (nchunks > 0) {
-    index_hist_kernel<<<grid, warps * 32, smem, s>>>(topk_idx, T, static_cast<int>(E),
-                                                     static_cast<int>(K), chunk_hist, status);
-    FMOE_CUDA(cudaGetLastError());
-  }
-  index_scan_kernel<<<1, 1024, sizeof(int32_t) * static_cast<size_t>(E), s>>>(chunk_hist, nchunks, static_cast<int>(E),
-                                               static_cast<int>(world), counts, offsets, rank_counts);
+  index_hist_kernel<<<grid, warps * 32, sizeof(int32_t) * static_cast<size_t>(E) * warps, s>>>(
+      topk_idx, T, e, static_cast<int>(K), chunk_hist, status);
   FMOE_CUDA(cudaGetLastError());
-  if (nchunks > 0) {
-    index_place_kernel<<<grid, warps * 32, smem, s>>>(topk_idx, topk_w, w_dtype, T,
-                                                      static_cast<int>(E), static_cast<int>(K),
-                                                      chunk_hist, offsets, reverse_map, sorted_w,
-                                                      slot_of);
-    FMOE_CUDA(cudaGetLastError());
-  }
-  return FMOE_OK;
+  index_chunk_scan_kernel<<<(e + 7) / 8, 256, 0, s>>>(chunk_hist, nchunks, e, totals);
+  FMOE_CUDA(cudaGetLastError());
+  index_place_kernel<<<grid, warps * 32, sizeof(int32_t) * (static_cast<size_t>(E) * warps + E + 1), s>>>(
+      topk_idx, topk_w, w_dtype, T, e, static_cast<int>(K), static_cast<int>(world), chunk_hist, totals,
+      counts, offsets, rank_counts, reverse_map, sorted_w, slot_of);
+  return check_launch("index_place_kernel");
 }
