@@ -177,6 +177,7 @@ def cpu_pass(host, T, D):
     import oracle
 
     experts, idx, w = host
+    oracle.use_all_cores()
     ex = [e.view(torch.int16).numpy().view(np.uint16) for e in experts]
     t0 = time.perf_counter()
     oracle.combine_bf16(ex, idx.numpy(), w.view(torch.int16).numpy().view(np.uint16), T)

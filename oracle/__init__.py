@@ -49,6 +49,16 @@ def num_threads() -> int:
     return int(_c().oracle_num_threads())
 
 
+def use_all_cores() -> int:
+    """Lets the C oracle use every core this process may run on (an inherited
+    OMP_NUM_THREADS=1, as torchrun sets it, would otherwise pin it to one). Returns the count."""
+    import os
+
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    _c().oracle_set_num_threads(ctypes.c_int(n))
+    return num_threads()
+
+
 def _ptr(a: np.ndarray) -> ctypes.c_void_p:
     return ctypes.c_void_p(a.ctypes.data)
 
