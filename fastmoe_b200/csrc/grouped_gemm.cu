@@ -29,7 +29,7 @@ constexpr int kBBytes = kBN * kBK * 2;        // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kGemmThreads = 192;
 constexpr int kMaxExperts = 1024;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 24;  // probes per wait before giving up (about a second)
 
 struct GemmArgs {
   const int64_t* offsets;  // [E] first row of each expert in A / C
@@ -44,6 +44,8 @@ struct GemmArgs {
   int w_rows_per_expert;   // rows of the weight tensor per expert (N, or 2*ff for SwiGLU)
   int up_row_offset;       // SwiGLU: row of the first "up" weight inside an expert (= ff), else 128
   int swiglu;
+  int skip_loads;  // test hook: the producer issues nothing, so every consumer wait runs out
+  uint32_t spin_limit;
   int32_t* status;
 };
 
@@ -61,10 +63,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-// Bounded wait: false after kSpinLimit unsuccessful probes.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait: false after `limit` unsuccessful probes, or once another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -220,12 +223,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // ---- TMA producer ---------------------------------------------------------------
     int stage = 0;
     uint32_t phase = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < total_tiles && !a.skip_loads; tile += gridDim.x) {
       const TileCoord c = locate_tile(tile, mb_prefix, a);
       const int w_row0 = c.expert * a.w_rows_per_expert + c.nb * (a.swiglu ? 128 : kBN);
       const int w_row1 = w_row0 + a.up_row_offset;
       for (int kb = 0; kb < a.k_blocks; ++kb) {
-        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) goto timed_out;
+        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
         mbar_expect_tx(&full[stage], kStageBytes);
         tma_load_2d(smem_a + stage * kABytes, &map_a, kb * kBK, static_cast<int>(c.row0), &full[stage]);
         tma_load_2d(smem_b + stage * kBBytes, &map_w, kb * kBK, w_row0, &full[stage]);
@@ -241,11 +244,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) goto timed_out;
+      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
       tcgen05_fence_after();
       const uint32_t tmem_d = tmem_base + acc * kBN;
       for (int kb = 0; kb < a.k_blocks; ++kb) {
-        if (!mbar_wait(&full[stage], phase, abort_flag)) goto timed_out;
+        if (!mbar_wait(&full[stage], phase, abort_flag, a.spin_limit)) goto timed_out;
         tcgen05_fence_after();
         const uint64_t da = smem_desc(smem_u32(smem_a + stage * kABytes));
         const uint64_t db = smem_desc(smem_u32(smem_b + stage * kBBytes));
@@ -267,7 +270,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const TileCoord c = locate_tile(tile, mb_prefix, a);
-      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) goto timed_out;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, a.spin_limit)) goto timed_out;
       tcgen05_fence_after();
       const int row = quarter * 32 + lane;
       const bool valid = row < c.rows;
@@ -338,6 +341,10 @@ done:
 // SMs the persistent grid may occupy (fmoe_tune "gemm_sms"). Leaving a few SMs free lets
 // NCCL's copy kernels run beside the GEMM instead of waiting for its CTAs to retire.
 int g_gemm_sms = kNumSMs;
+// Test hooks (fmoe_tune "gemm_skip_loads", "gemm_spin_limit"): make the bounded waits run out
+// on purpose, with a short limit, to exercise the give-up path without hanging anything.
+int g_gemm_skip_loads = 0;
+int g_gemm_spin_limit = static_cast<int>(kSpinLimit);
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -414,6 +421,8 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   g.w_rows_per_expert = static_cast<int>(N);
   g.up_row_offset = static_cast<int>(swiglu ? N / 2 : 128);
   g.swiglu = swiglu ? 1 : 0;
+  g.skip_loads = g_gemm_skip_loads;
+  g.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
   g.status = status;
 
   const size_t smem = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + sizeof(int) * (E + 2);

@@ -65,7 +65,10 @@ const char* fmoe_status_name(int status);
  * 1, 2, 4), "gather_threads" (threads per CTA, 0 = auto, else a multiple of 32
  * up to 256), "gather_ctas_per_sm" (-1 = auto, 0 = one CTA per work item,
  * else a persistent grid of 148 x value CTAs), "bwd_ctas_per_sm", "gemm_sms" (SMs the
- * grouped GEMM's persistent grid occupies, 1..148; fewer leaves room for NCCL kernels). */
+ * grouped GEMM's persistent grid occupies, 1..148; fewer leaves room for NCCL kernels).
+ * Test hooks: "gemm_spin_limit" (probes per bounded device-side wait) and
+ * "gemm_skip_loads" (1 = the GEMM's producer issues no loads, so its consumers' waits run
+ * out and the kernel reports FMOE_STATUS_WAIT_TIMEOUT instead of computing). */
 int fmoe_tune(const char* key, int value);
 
 /* ---- combine: scatter form ---------------------------------------------- */

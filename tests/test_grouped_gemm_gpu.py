@@ -111,3 +111,27 @@ def test_row_map_scatters_the_output_rows():
     ref = torch.empty_like(fused)
     ref[perm] = experts.grouped_gemm(a, wgu, off, cnt, swiglu=True)
     assert torch.equal(fused, ref)
+
+
+def test_bounded_waits_give_up_and_report_instead_of_hanging():
+    """Failure detection without a fault: with the producer told to load nothing, the MMA and
+    epilogue roles' mbarrier waits run out (short limit), the kernel sets the WAIT_TIMEOUT status
+    bit, releases its tensor memory and returns; the context stays usable and the next launch is
+    correct."""
+    from fastmoe_b200 import _lib
+
+    a, w, off, cnt = _case([300, 100], 256, 256, False, seed=11)
+    _lib.tune("gemm_spin_limit", 1 << 12)
+    _lib.tune("gemm_skip_loads", 1)
+    try:
+        experts.grouped_gemm(a, w, off, cnt)
+        torch.cuda.synchronize()
+        assert ops.read_status() & 8
+    finally:
+        _lib.tune("gemm_skip_loads", 0)
+        _lib.tune("gemm_spin_limit", 1 << 24)
+    c = experts.grouped_gemm(a, w, off, cnt)
+    torch.cuda.synchronize()
+    assert ops.read_status() == 0
+    ref = _reference(a, w, [300, 100], False)
+    assert float((c.float() - ref).abs().max() / ref.abs().max()) <= 1e-2

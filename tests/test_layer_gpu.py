@@ -173,3 +173,26 @@ def test_swiglu_layer_matches_fp32_reference(impl):
     assert err <= 2e-2, err
     assert x.grad is not None and moe.experts.w_gate_up.grad is not None and moe.router.weight.grad is not None
     assert torch.isfinite(x.grad.float()).all()
+
+
+def test_pipelined_block_matches_unpipelined_computation():
+    """PipelinedMoEBlock (micro-batches on side streams) against the same block evaluated in one
+    piece on the current stream; also with 4 micro-batches and SwiGLU experts."""
+    from fastmoe_b200.models.tiny_model import PipelinedMoEBlock
+
+    torch.manual_seed(1)
+    for n_mb, expert_type, dtype in ((2, "gelu", torch.float32), (4, "swiglu", torch.bfloat16)):
+        s0, s1 = torch.cuda.Stream(), torch.cuda.Stream()
+        blk = PipelinedMoEBlock(256, 4, 128, 8, 2, s0, s1, num_micro_batches=n_mb, expert_type=expert_type)
+        blk = blk.to(DEV).to(dtype)
+        x = torch.randn(8, 32, 256, device=DEV, dtype=dtype)
+        with torch.no_grad():
+            out = blk(x)
+            torch.cuda.synchronize()
+            r = x + blk.attn(blk.norm1(x))
+            ref = torch.cat([blk.moe(c) for c in blk.norm2(r).chunk(n_mb, 0)], 0) + r
+        assert out.shape == x.shape
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        err = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
+        assert err <= tol, (n_mb, expert_type, err)
+    assert ops.read_status() == 0
