@@ -99,7 +99,7 @@ def measured_peak():
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.05):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -405,9 +405,9 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
     more (22.5 GB / world each time) and thins the rows per expert: measured, the grouped
     GEMMs for 65536 rows take 4.52 / 4.66 / 5.51 ms in 1 / 2 / 4 launches at 32 experts per
     rank and 5.08 / 5.43 / 5.91 ms at 64, and at 2 and 4 ranks one micro-batch was fastest
-    (2 ranks: 8.7 ms against 10.2 ms with two). The default is therefore 1 micro-batch below
-    8 ranks and 2 at 8 ranks; --micro-batches overrides it (the configuration's nominal
-    value is 4). Returns tokens/s over all ranks (max time over ranks)."""
+    (2 ranks: 8.7 ms against 10.2 ms with two; 8 ranks: 8.5 ms against 9.0 ms). The default is
+    therefore 1 micro-batch; --micro-batches overrides it (the configuration's nominal value
+    is 4). Returns tokens/s over all ranks (max time over ranks)."""
     import torch
     import torch.distributed as dist
 
@@ -416,7 +416,7 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
 
     dev = torch.device("cuda", local_rank)
     T, D, FF, E, K = 8192, 7168, 2048, 256, 8
-    MB = micro_batches or (2 if world >= 8 else 1)
+    MB = micro_batches or 1
     with torch.device(dev):
         moe = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST, expert_type="swiglu")
     moe = moe.to(torch.bfloat16)
@@ -463,6 +463,27 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms[0]) / steps
     assert all(bool(torch.isfinite(o.float()).all()) for o in outs)
+    cpu_baseline = None
+    if rank == 0:  # CPU baseline: the expert FFN of a 256-token sample through torch's CPU matmul
+        import os
+
+        cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        torch.set_num_threads(cores)
+        Ts, Es = 256, 8  # 256 tokens x top-8 = 2048 routed rows, spread over 8 experts
+        g = torch.Generator().manual_seed(0)
+        xs = torch.randn(Ts * K, D, generator=g)
+        wgu = torch.empty(Es, 2 * FF, D).normal_(0, 0.02, generator=g)
+        wd = torch.empty(Es, D, FF).normal_(0, 0.02, generator=g)
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            for e, chunk in enumerate(xs.chunk(Es, 0)):
+                h = chunk @ wgu[e].t()
+                (torch.nn.functional.silu(h[:, :FF]) * h[:, FF:]) @ wd[e].t()
+        cpu_s = time.perf_counter() - t0
+        cpu_baseline = {"value": Ts / cpu_s, "unit": "tokens/s", "cores": cores, "kind": "port", "ms": cpu_s * 1e3,
+                        "sample": "expert FFN only (the dominant cost) for 256 tokens x top-8 = 2048 routed rows "
+                                  "over 8 experts, fp32 torch CPU matmul"}  # fmt: skip
+        del xs, wgu, wd
     gemm_flops = 6 * T * K * D * FF  # per rank and step: three D x FF products per routed row
     a2a_bytes = T * K * D * 2 * (world - 1) / world  # leaving each GPU, per direction
     del moe
@@ -475,6 +496,7 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
         "gemm_flops_per_rank": gemm_flops,
         "a2a_bytes_out_per_rank_per_direction": a2a_bytes,
         "experts_per_rank": e_local,
+        "cpu_baseline": cpu_baseline,
         "config": {"D": D, "ff": FF, "E": E, "top_k": K, "experts": "swiglu", "weights": "N(0,0.02) seeded per expert"},
     }  # fmt: skip
 
@@ -580,8 +602,10 @@ def run_cfg4(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     T, D, E, K = CFG4[args.workload]
     N, s = T * K, 2
-    idx, w = routing_uniform(T, E, K, seed=rank)
-    idx, gate = idx.to(dev), w.to(dev).bfloat16().requires_grad_(True)
+    idx_cpu, w_cpu = routing_uniform(T, E, K, seed=rank)
+    idx, gate = idx_cpu.to(dev), w_cpu.to(dev).bfloat16().requires_grad_(True)
+    logits = torch.randn(T, E, generator=torch.Generator(device=dev).manual_seed(7 + rank), device=dev,
+                         dtype=torch.bfloat16)  # router logits, only to time the top-k/softmax kernel
     gen = torch.Generator(device=dev).manual_seed(rank)
     x = torch.randn(T, D, generator=gen, device=dev, dtype=torch.bfloat16).requires_grad_(True)
     grad_out = torch.randn(T, D, generator=gen, device=dev, dtype=torch.bfloat16)
@@ -596,6 +620,7 @@ def run_cfg4(args, rank, world, local_rank):
 
     def step():
         x.grad = gate.grad = None
+        routing.route_topk(logits, K)  # timed; the chain below uses the fixed uniform routing
         ix = routing.build_index(idx, gate, E)
         permuted = routing.permute_rows(x, ix.slot_of, K)
         out = ops.grouped_weighted_scatter_add([permuted], ix.reverse_map, ix.sorted_w, (T, D))
@@ -638,6 +663,28 @@ def run_cfg4(args, rank, world, local_rank):
             entry.update(algorithmic_bytes=alg[name], achieved=alg[name] / ms / 1e6, frac=alg[name] / ms / 1e6 / peak)
         kernels[name] = entry
     top = max(alg, key=lambda k: kernels[k]["ms"])
+
+    # CPU baseline: the oracle port of the same chain (fp32 arithmetic) on the first 2048 tokens
+    import numpy as np
+
+    import oracle
+
+    oracle.use_all_cores()
+    Ts = min(T, 2048)
+    o_ix = oracle.build_index(idx_cpu[:Ts].numpy(), w_cpu[:Ts].numpy(), E)
+    xs = x.detach()[:Ts].float().cpu().numpy()
+    gs = grad_out[:Ts].float().cpu().numpy()
+    t0 = time.perf_counter()
+    perm = oracle.permute(xs, o_ix["reverse_map"])
+    oracle.combine([perm], o_ix["reverse_map"], o_ix["sorted_w"], Ts)
+    g_rows, _ = oracle.combine_bwd(perm, o_ix["reverse_map"], o_ix["sorted_w"], gs)
+    oracle.permute_bwd(g_rows, o_ix["reverse_map"], Ts)
+    cpu_s = time.perf_counter() - t0
+    cpu_baseline = {"value": total_bytes * Ts / T / cpu_s / 1e9, "unit": UNIT, "cores": oracle.num_threads(),
+                    "kind": "port", "ms": cpu_s * 1e3,
+                    "sample": f"the first {Ts} of {T} tokens, one pass of permute + combine + both backwards "
+                              "in fp32; bytes counted as in the bf16 workload"}  # fmt: skip
+    del np
     line = {
         "metric": "dispatch_combine_hbm_gbs", "value": total_bytes * world * args.steps / (elapsed_ms / 1e3) / 1e9,
         "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -648,7 +695,7 @@ def run_cfg4(args, rank, world, local_rank):
         "e2e": None, "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": top, "achieved": kernels[top]["achieved"], "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": kernels[top]["frac"], "traffic": None},
-        "kernels": kernels, "clocks": clocks.summary(),
+        "kernels": kernels, "cpu_baseline": cpu_baseline, "clocks": clocks.summary(),
     }  # fmt: skip
     print(json.dumps(line), flush=True)
 

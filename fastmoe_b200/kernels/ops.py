@@ -60,6 +60,8 @@ _mode = os.environ.get("FASTMOE_B200_COMBINE", "gather")
 _check = os.environ.get("FASTMOE_B200_CHECK", "0") == "1"
 
 _status_words: dict[int, torch.Tensor] = {}
+# (device, addresses + offsets + sizes) -> device arrays of prepare_grouped_metadata, a few entries
+_table_cache: dict = {}
 
 
 def combine_mode() -> str:
@@ -167,16 +169,35 @@ def prepare_grouped_metadata(expert_tensors, device):
     offsets = list(itertools.accumulate(sizes, initial=0))
     run = offsets.pop()
     device = torch.device(device)
+    table = ptrs + offsets + sizes
     if device.type == "cuda":
-        # pinned staging + asynchronous copy: the host never waits for the stream to drain
-        staging = torch.empty(3 * num_experts, dtype=torch.int64, pin_memory=True)
-        staging.numpy()[:] = ptrs + offsets + sizes
-        packed = staging.to(device, non_blocking=True)
+        # The device arrays are a pure function of (addresses, sizes): when the same matrices
+        # come back (the caching allocator hands out the same blocks step after step) the
+        # arrays of the previous call are reused and nothing is copied.
+        key = (device.index, tuple(table))
+        cached = _table_cache.get(key)
+        if cached is None:
+            # pinned staging + asynchronous copy: the host never waits for the stream to drain
+            staging = torch.empty(3 * num_experts, dtype=torch.int64, pin_memory=True)
+            staging.numpy()[:] = table
+            packed = staging.to(device, non_blocking=True)
+            cached = (packed[:num_experts], packed[2 * num_experts :].to(torch.int32),
+                      packed[num_experts : 2 * num_experts], torch.cuda.current_stream(device), packed)  # fmt: skip
+            if len(_table_cache) >= 8:
+                _table_cache.pop(next(iter(_table_cache)))
+            _table_cache[key] = cached
+        elif cached[3] != torch.cuda.current_stream(device):
+            # built on another stream: order this stream after the copy that filled it
+            current = torch.cuda.current_stream(device)
+            current.wait_stream(cached[3])
+            cached[4].record_stream(current)  # keep the allocator from recycling it under this stream
+            cached[1].record_stream(current)
+        ptr_table, chunk_sizes, expert_offsets = cached[:3]
     else:
-        packed = torch.from_numpy(np.array(ptrs + offsets + sizes, dtype=np.int64))
-    ptr_table = packed[:num_experts]
-    expert_offsets = packed[num_experts : 2 * num_experts]
-    chunk_sizes = packed[2 * num_experts :].to(torch.int32)
+        packed = torch.from_numpy(np.array(table, dtype=np.int64))
+        ptr_table = packed[:num_experts]
+        expert_offsets = packed[num_experts : 2 * num_experts]
+        chunk_sizes = packed[2 * num_experts :].to(torch.int32)
     return GroupedMetadata(ptr_table, chunk_sizes, expert_offsets, max(sizes), num_experts,
                            run, dim, dtype, keep)  # fmt: skip
 
