@@ -3,6 +3,8 @@
 // table. Stands in for the per-row lookups of the reference kernel
 // (src/fastmoe/kernels/ops.py:129-163) so that the data kernels stream rows
 // without touching idx, w, offsets or the pointer table.
+#include <cooperative_groups.h>
+
 #include "plan.cuh"
 
 namespace fmoe {
@@ -117,6 +119,143 @@ __global__ void __launch_bounds__(256) plan_finalize_kernel(const PlanArgs a) {
   a.p.w_sorted[slot] = load_scalar_as_float(a.w, g, a.w_dtype);
 }
 
+// ---- all four steps in one cooperative launch -----------------------------------------
+// The separate kernels above are launch-latency bound (a few microseconds each for 64k
+// rows). This kernel runs the same steps with grid-wide barriers in between: zero the
+// histogram, count, scan (every CTA scans 512-wide pieces, then adds the prefix of the piece
+// totals, which it recomputes locally), place, finalize. The piece totals borrow the
+// row_of_slot section, which is not written before the last step.
+constexpr int kFusedThreads = 512;
+constexpr int kFusedMaxPieces = 8192;  // pieces of 512 targets: T up to 4M
+
+__device__ __forceinline__ int32_t block_exclusive_scan(int32_t v, int32_t* warp_sums, int32_t& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int32_t incl = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int32_t n = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += n;
+  }
+  __syncthreads();  // warp_sums may still be read from the previous call
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int32_t s = lane < (kFusedThreads >> 5) ? warp_sums[lane] : 0;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int32_t n = __shfl_up_sync(0xffffffffu, s, d);
+      if (lane >= d) s += n;
+    }
+    warp_sums[lane] = s;
+  }
+  __syncthreads();
+  total = warp_sums[(kFusedThreads >> 5) - 1];
+  return (warp == 0 ? 0 : warp_sums[warp - 1]) + incl - v;
+}
+
+__global__ void __launch_bounds__(kFusedThreads) plan_fused_kernel(const PlanArgs a) {
+  namespace cg = cooperative_groups;
+  cg::grid_group grid = cg::this_grid();
+  __shared__ int32_t warp_sums[32];
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(kFusedThreads) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * kFusedThreads;
+  int32_t* piece_total = a.p.row_of_slot;
+  const int64_t pieces = (a.T + kFusedThreads - 1) / kFusedThreads;
+
+  for (int64_t t = tid; t < a.T; t += nthreads) a.p.cnt[t] = 0;
+  grid.sync();
+
+  int flags = 0;
+  for (int64_t g = tid; g < a.N; g += nthreads) {
+    const int64_t t = load_index(a.idx, g, a.idx_type);
+    if (t < 0 || t >= a.T) {
+      a.p.rank[g] = -1;
+      flags |= FMOE_STATUS_BAD_INDEX;
+    } else {
+      a.p.rank[g] = atomicAdd(&a.p.cnt[t], 1);
+    }
+  }
+  grid.sync();
+
+  for (int64_t piece = blockIdx.x; piece < pieces; piece += gridDim.x) {
+    const int64_t t = piece * kFusedThreads + threadIdx.x;
+    const int32_t v = t < a.T ? a.p.cnt[t] : 0;
+    int32_t total;
+    const int32_t excl = block_exclusive_scan(v, warp_sums, total);
+    if (t < a.T) a.p.seg_off[t] = excl;
+    if (threadIdx.x == 0) piece_total[piece] = total;
+  }
+  grid.sync();
+
+  for (int64_t piece = blockIdx.x; piece < pieces; piece += gridDim.x) {
+    // prefix of the totals of all earlier pieces, summed by this CTA
+    int32_t part = 0;
+    for (int64_t q = threadIdx.x; q < piece; q += kFusedThreads) part += piece_total[q];
+    int32_t base;
+    block_exclusive_scan(part, warp_sums, base);
+    const int64_t t = piece * kFusedThreads + threadIdx.x;
+    if (t < a.T) a.p.seg_off[t] += base;
+    if (piece == pieces - 1 && threadIdx.x == 0) a.p.seg_off[a.T] = base + piece_total[piece];
+  }
+  grid.sync();
+
+  for (int64_t g = tid; g < a.N; g += nthreads) {
+    const int32_t r = a.p.rank[g];
+    if (r < 0) continue;
+    const int64_t t = load_index(a.idx, g, a.idx_type);
+    a.p.seg_rows[a.p.seg_off[t] + r] = static_cast<int32_t>(g);
+  }
+  grid.sync();
+
+  for (int64_t g = tid; g < a.N; g += nthreads) {
+    int32_t r = a.p.rank[g];
+    if (r < 0) continue;
+    const int64_t t = load_index(a.idx, g, a.idx_type);
+    const int32_t beg = a.p.seg_off[t], end = a.p.seg_off[t + 1];
+    if (end - beg <= kPlanStableCap) {
+      r = 0;
+      for (int32_t j = beg; j < end; ++j) r += (a.p.seg_rows[j] < g) ? 1 : 0;
+    }
+    const int32_t slot = beg + r;
+    int64_t addr = 0;
+    const int e = find_expert(a.expert_offsets, a.E, g);
+    const int64_t local = g - a.expert_offsets[e];
+    if (local < 0 || local >= a.chunk_sizes[e]) {
+      flags |= FMOE_STATUS_BAD_EXPERT;
+    } else {
+      const int64_t base = a.ptr_table[e];
+      if (base == 0)
+        flags |= FMOE_STATUS_NULL_PTR;
+      else
+        addr = base + local * a.D * a.elem_bytes;
+    }
+    // row_of_slot doubles as the piece totals: they were last read before the previous barrier
+    a.p.row_of_slot[slot] = static_cast<int32_t>(g);
+    a.p.src_sorted[slot] = addr;
+    a.p.w_sorted[slot] = load_scalar_as_float(a.w, g, a.w_dtype);
+  }
+  if (flags != 0 && a.status != nullptr) atomicOr(a.status, flags);
+}
+
+// Cooperative grid size for the current device (0 = cooperative launch not usable), cached.
+static int fused_grid_limit() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int coop = 0, per_sm = 0, sms = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (coop && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, plan_fused_kernel, kFusedThreads, 0) ==
+                    cudaSuccess &&
+        per_sm > 0)
+      cached[dev] = per_sm * sms;
+    else
+      cached[dev] = -1;
+  }
+  return cached[dev] > 0 ? cached[dev] : 0;
+}
+
 }  // namespace fmoe
 
 extern "C" size_t fmoe_combine_plan_bytes(int64_t N, int64_t T) {
@@ -164,6 +303,17 @@ extern "C" int fmoe_combine_plan(const int64_t* ptr_table, const int32_t* chunk_
   a.p = pv;
   a.status = status;
 
+  const int64_t pieces = (T + kFusedThreads - 1) / kFusedThreads;
+  const int limit = N > 0 ? fused_grid_limit() : 0;
+  if (limit > 0 && pieces <= N && pieces <= kFusedMaxPieces) {
+    // one cooperative launch; the piece totals fit into the row_of_slot section (N ints)
+    const int64_t want = ((N > T ? N : T) + kFusedThreads - 1) / kFusedThreads;
+    const int grid = static_cast<int>(want < limit ? want : limit);
+    void* params[] = {&a};
+    FMOE_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(plan_fused_kernel), dim3(grid),
+                                          dim3(kFusedThreads), params, 0, s));
+    return FMOE_OK;
+  }
   // cnt and seg_off are adjacent sections: one memset zeroes both (seg_off must
   // be all zero when N == 0 or T is tiny, the scan overwrites it otherwise)
   FMOE_CUDA(cudaMemsetAsync(pv.seg_off, 0,
