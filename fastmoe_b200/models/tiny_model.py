@@ -311,14 +311,21 @@ def pipelined_moe_forward(moe, inputs, streams):
 
     if n:
         dispatch(0)
+    experts_done = None
     for i in range(n):
         if i + 1 < n:
             dispatch(i + 1)
         with torch.cuda.stream(streams[i]):
             _, _, _, rev, w, shape = gated[i]
             recv, recv_splits, send_splits, tokens = dispatched[i]
+            if experts_done is not None:
+                # one micro-batch's experts at a time: two persistent GEMMs sharing the SMs
+                # finish later than either alone and delay the return exchange they feed
+                streams[i].wait_event(experts_done)
             with record_function(f"S{i}: Experts {i}"):
                 eo = moe.compute_experts(recv, tokens)
+            experts_done = torch.cuda.Event()
+            experts_done.record()
             with record_function(f"S{i}: Combine {i}"):
                 fd = moe.combine_exchange(eo, recv_splits, send_splits)
             with record_function(f"S{i}: Finalize {i}"):

@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory by running the REFERENCE's own
 CPU/PyTorch path (polkadot21/fastmoe, imported unchanged from a source checkout).
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference checkout exists only where the fixtures are made; tests read the
 committed .npz files and never import the reference. Inputs are stored in the
@@ -20,7 +20,9 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py /path/to/a/checkout/of/polkadot21/fastmoe")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF / "src"))
 
 sys.path.insert(0, str(HERE))
