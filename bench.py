@@ -326,7 +326,7 @@ def run_ours(args, rank, world, local_rank):
         n_rows = wl.N
         del wl, out, arena
         torch.cuda.empty_cache()
-        ep = ep_layer_bench(rank, world, local_rank, min(args.steps, 20), min(args.warmup, 5))
+        ep = ep_layer_bench(rank, world, local_rank, min(args.steps, 20), min(args.warmup, 5), None, args.ep_mode)
     else:
         n_rows = wl.N
 
@@ -397,7 +397,7 @@ def run_ours(args, rank, world, local_rank):
 EP_WORKLOAD = "ep_moe_layer_cfg5_bf16_8192tok_D7168_E256_top8_swiglu2048"
 
 
-def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
+def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, mode="fused"):
     """Expert-parallel MoE layer forward: 8192 tokens per rank, D=7168, 256 experts sharded
     evenly over the ranks, top-8 softmax router, SwiGLU experts 7168->2048->7168, weights
     N(0, 0.02). Micro-batches run on their own streams, the exchange of one overlapping the
@@ -435,7 +435,28 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
     streams = [torch.cuda.Stream(device=dev) for _ in range(MB)]
     main = torch.cuda.current_stream()
 
+    # With several ranks the default is the fused exchange: dispatch by peer stores from the
+    # permute kernel, return trip in the down-projection's epilogue, no payload collective and
+    # no host synchronisation (fastmoe_b200/ep_fused.py). "nccl" selects the all-to-all path.
+    fused, ep_mode = None, "single rank"
+    if world > 1:
+        ep_mode = "nccl all_to_all"
+        if mode == "fused":
+            try:
+                from fastmoe_b200.ep_fused import FusedExpertParallel
+
+                fused = FusedExpertParallel(moe, max_tokens=T)
+                ep_mode = "fused peer stores"
+            except Exception as exc:  # symmetric memory unavailable: every rank falls back alike
+                ep_mode = f"nccl all_to_all (fused path unavailable: {type(exc).__name__})"
+        ok = torch.tensor([1 if fused is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            fused = None
+
     def step():
+        if fused is not None:
+            return [fused(x.view(1, T, D))]
         for s in streams:
             s.wait_stream(main)
         with torch.no_grad():
@@ -486,7 +507,7 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
         del xs, wgu, wd
     gemm_flops = 6 * T * K * D * FF  # per rank and step: three D x FF products per routed row
     a2a_bytes = T * K * D * 2 * (world - 1) / world  # leaving each GPU, per direction
-    del moe
+    del moe, fused
     torch.cuda.empty_cache()
     return {
         "tokens_per_s": T * world / (ms / 1e3),
@@ -496,6 +517,7 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None):
         "gemm_flops_per_rank": gemm_flops,
         "a2a_bytes_out_per_rank_per_direction": a2a_bytes,
         "experts_per_rank": e_local,
+        "exchange": ep_mode,
         "cpu_baseline": cpu_baseline,
         "config": {"D": D, "ff": FF, "E": E, "top_k": K, "experts": "swiglu", "weights": "N(0,0.02) seeded per expert"},
     }  # fmt: skip
@@ -509,7 +531,7 @@ def run_ep(args, rank, world, local_rank):
         from fastmoe_b200 import _lib
 
         _lib.tune("gemm_sms", args.gemm_sms)
-    r = ep_layer_bench(rank, world, local_rank, args.steps, args.warmup, args.micro_batches)
+    r = ep_layer_bench(rank, world, local_rank, args.steps, args.warmup, args.micro_batches, args.ep_mode)
     if rank != 0:
         return
     peak, kind = measured_tflops()
@@ -708,6 +730,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(CFG4) + sorted(GEMM) + [EP_WORKLOAD], default=DEFAULT_WORKLOAD)
     ap.add_argument("--micro-batches", type=int, default=None, help="expert-parallel layer: micro-batches per step")
+    ap.add_argument("--ep-mode", choices=["fused", "nccl"], default="fused",
+                    help="expert-parallel layer with several ranks: fused peer-store exchange or NCCL all-to-all")
     ap.add_argument("--gemm-sms", type=int, default=None, help="expert-parallel layer: SMs for the grouped GEMM")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel layer part of the default run")
     args = ap.parse_args()

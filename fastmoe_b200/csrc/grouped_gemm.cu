@@ -35,6 +35,7 @@ struct GemmArgs {
   const int64_t* offsets;  // [E] first row of each expert in A / C
   const int64_t* counts;   // [E] rows of each expert
   const int64_t* c_row_map;  // optional [R]: row of C that receives the result of A's row r (nullptr = r)
+  const int64_t* c_row_ptrs;  // optional [R]: ADDRESS of the output row of A's row r (may be peer memory)
   __nv_bfloat16* C;
   int64_t ldc;             // row stride of C in elements
   int64_t R;               // rows of A
@@ -278,9 +279,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // destination row: the same row as in A, or wherever the row map sends it (rows are
       // stored one per thread, so scattering them costs nothing extra)
       int64_t out_row = c.row0 + row;
-      if (valid && a.c_row_map != nullptr) out_row = a.c_row_map[out_row];
+      __nv_bfloat16* out_base = a.C;
+      if (valid && a.c_row_ptrs != nullptr) {
+        // the row lives wherever the table says, e.g. in the buffer of the GPU that owns the
+        // token: the return trip of the expert-parallel layer rides on the epilogue's stores
+        out_base = reinterpret_cast<__nv_bfloat16*>(a.c_row_ptrs[out_row]);
+        out_row = 0;
+        if (out_base == nullptr) out_base = a.C, out_row = c.row0 + row;
+      } else if (valid && a.c_row_map != nullptr) {
+        out_row = a.c_row_map[out_row];
+      }
       if (a.swiglu) {
-        __nv_bfloat16* crow = a.C + out_row * a.ldc + static_cast<int64_t>(c.nb) * 128;
+        __nv_bfloat16* crow = out_base + out_row * a.ldc + static_cast<int64_t>(c.nb) * 128;
 #pragma unroll 1
         for (int c0 = 0; c0 < 128; c0 += 32) {
           uint32_t g[32], u[32];
@@ -299,7 +309,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       } else {
-        __nv_bfloat16* crow = a.C + out_row * a.ldc + static_cast<int64_t>(c.nb) * kBN;
+        __nv_bfloat16* crow = out_base + out_row * a.ldc + static_cast<int64_t>(c.nb) * kBN;
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN; c0 += 32) {
           uint32_t r[32];
@@ -383,8 +393,9 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t co
 using namespace fmoe;
 
 extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
-                                 const int64_t* counts, const int64_t* c_row_map, int64_t E, int64_t R,
-                                 int64_t N, int64_t K, int swiglu, int32_t* status, void* stream) {
+                                 const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
+                                 int64_t E, int64_t R, int64_t N, int64_t K, int swiglu, int32_t* status,
+                                 void* stream) {
   FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm: bad sizes");
   FMOE_REQUIRE(E <= kMaxExperts, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: supports E <= %d", kMaxExperts);
   FMOE_REQUIRE(K % kBK == 0, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: K=%lld must be a multiple of %d",
@@ -399,7 +410,8 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   FMOE_REQUIRE(R < (1ll << 31) && E * N < (1ll << 31), FMOE_ERR_UNSUPPORTED,
                "fmoe_grouped_gemm: R and E*N must fit in int32");
   if (E == 0 || R == 0) return FMOE_OK;
-  FMOE_REQUIRE(a && w && c && offsets && counts, FMOE_ERR_ARG, "fmoe_grouped_gemm: null pointer argument");
+  FMOE_REQUIRE(a && w && (c || c_row_ptrs) && offsets && counts, FMOE_ERR_ARG,
+               "fmoe_grouped_gemm: null pointer argument");
   FMOE_REQUIRE(aligned_to(a, 16) && aligned_to(w, 16) && aligned_to(c, 16), FMOE_ERR_ARG,
                "fmoe_grouped_gemm: a, w and c must be 16-byte aligned");
   CUtensorMap map_a, map_w;
@@ -412,6 +424,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   g.offsets = offsets;
   g.counts = counts;
   g.c_row_map = c_row_map;
+  g.c_row_ptrs = c_row_ptrs;
   g.C = static_cast<__nv_bfloat16*>(c);
   g.ldc = swiglu ? N / 2 : N;
   g.R = R;

@@ -32,18 +32,21 @@ def _check(a, w, offsets, counts):
         raise ValueError("offsets and counts need one entry per expert")
 
 
-def _launch(a, w, offsets, counts, swiglu, row_map=None, covers_all_rows=False):
+def _launch(a, w, offsets, counts, swiglu, row_map=None, covers_all_rows=False, row_ptrs=None):
     a, w = a.contiguous(), w.contiguous()
     R, K = a.shape
     E, N, _ = w.shape
     cols = N // 2 if swiglu else N
-    if covers_all_rows or R == 0:
+    if row_ptrs is not None:
+        c = None  # every row goes where its table entry points
+    elif covers_all_rows or R == 0:
         c = torch.empty(R, cols, dtype=torch.bfloat16, device=a.device)
     else:  # rows that belong to no expert are never written: start from zeros so they are defined
         c = torch.zeros(R, cols, dtype=torch.bfloat16, device=a.device)
     ops._call(
-        "fmoe_grouped_gemm", 1, a.data_ptr(), w.data_ptr(), c.data_ptr(), offsets.data_ptr(),
-        counts.data_ptr(), row_map.data_ptr() if row_map is not None else None, E, R, N, K,
+        "fmoe_grouped_gemm", 1, a.data_ptr(), w.data_ptr(), c.data_ptr() if c is not None else None,
+        offsets.data_ptr(), counts.data_ptr(), row_map.data_ptr() if row_map is not None else None,
+        row_ptrs.data_ptr() if row_ptrs is not None else None, E, R, N, K,
         1 if swiglu else 0, _status_word(a.device).data_ptr(), _stream_ptr(a.device),
     )  # fmt: skip
     return c
@@ -102,3 +105,12 @@ def grouped_swiglu_ffn(x, w_gate_up, w_down, offsets, counts, row_map=None, cove
     hidden = grouped_gemm(x, w_gate_up, offsets, counts, swiglu=True, covers_all_rows=covers_all_rows)
     return grouped_gemm(hidden, w_down, offsets, counts, swiglu=False, row_map=row_map,
                         covers_all_rows=covers_all_rows)  # fmt: skip
+
+
+def grouped_gemm_to_rows(a, w, offsets, counts, row_ptrs):
+    """Plain grouped GEMM (no autograd) whose output row r is stored at the ADDRESS row_ptrs[r]
+    (int64 [R] on the device; the rows may live in other GPUs' memory). Returns nothing."""
+    _check(a, w, offsets, counts)
+    if row_ptrs.dtype != torch.int64 or row_ptrs.numel() < a.shape[0]:
+        raise ValueError("row_ptrs must be an int64 device tensor with one entry per row of a")
+    _launch(a, w, offsets, counts, False, row_ptrs=row_ptrs)

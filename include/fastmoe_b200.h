@@ -217,6 +217,25 @@ int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_of, void* gr
                      int64_t grad_x_row_stride, int64_t T, int64_t K, int64_t D,
                      int dtype, void* stream);
 
+/*
+ * Dispatch permute fused with the expert-parallel exchange: row (t,k) of x is written
+ * straight into the receive buffer of the GPU that owns its expert, at its final
+ * expert-major position, with plain peer stores over NVLink. It stands for the permute
+ * (tiny_model.py:133) plus the payload all-to-all (tiny_model.py:210-216) plus the
+ * regrouping on the receiver.
+ *   expert = topk_idx[t*K+k], dest GPU = expert / experts_per_rank,
+ *   dest row = dst_row0[expert] + (slot_of[t*K+k] - local_offsets[expert])
+ *   written to (char*)peer_bases[dest GPU] + dest row * D * sizeof(element)
+ * dst_row0, local_offsets int64[E]; peer_bases int64[world] (device array of mapped base
+ * addresses, own buffer included); rows at or beyond cap_rows are dropped and flagged with
+ * FMOE_STATUS_BAD_INDEX. The caller orders the consumers after all writers (a barrier).
+ */
+int fmoe_permute_peer_fwd(const void* x, int64_t x_row_stride, const int64_t* topk_idx,
+                          const int32_t* slot_of, const int64_t* local_offsets,
+                          const int64_t* dst_row0, const int64_t* peer_bases, int64_t T, int64_t K,
+                          int64_t D, int64_t E, int64_t experts_per_rank, int64_t cap_rows, int dtype,
+                          int32_t* status, void* stream);
+
 /* ---- expert FFN: grouped GEMM on tcgen05 ------------------------------------------ */
 /*
  * For every expert e with rows [offsets[e], offsets[e] + counts[e]) of A:
@@ -232,11 +251,16 @@ int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_of, void* gr
  * c_row_map (optional int64[R] on the device, NULL = identity) sends the result of A's row
  * r to row c_row_map[r] of C: the return-trip reordering of the expert-parallel layer
  * (expert-major rows back to source-rank-major) happens in the store, not in a copy.
+ * c_row_ptrs (optional int64[R] on the device, NULL = unused; takes precedence over
+ * c_row_map) gives the ADDRESS of the output row of A's row r, which may lie in another
+ * GPU's memory mapped into this process (plain peer stores; a zero entry falls back to C):
+ * the expert outputs then travel to the GPUs that own the tokens inside the epilogue.
  * A bounded device-side wait that gives up sets FMOE_STATUS_WAIT_TIMEOUT in `status`.
  */
 int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
-                      const int64_t* counts, const int64_t* c_row_map, int64_t E, int64_t R,
-                      int64_t N, int64_t K, int swiglu, int32_t* status, void* stream);
+                      const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
+                      int64_t E, int64_t R, int64_t N, int64_t K, int swiglu, int32_t* status,
+                      void* stream);
 
 /* ---- host-buffer call -------------------------------------------------------- */
 /*

@@ -95,6 +95,80 @@ def _worker(rank, world, port, q):
         raise
 
 
+def _fused_worker(rank, world, port, q):
+    failure = None
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                          TORCH_SYMM_MEM_DISABLE_MULTICAST="1")  # fmt: skip
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from fastmoe_b200.consts import MoEImplementation
+        from fastmoe_b200.ep_fused import FusedExpertParallel
+        from fastmoe_b200.kernels import ops
+        from fastmoe_b200.models.tiny_model import MoEFeedForward
+
+        T, D, FF, E, K = 640, 256, 128, 8, 2
+        moe = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST, expert_type="swiglu").to(dev).bfloat16()
+        g = torch.Generator(device=dev).manual_seed(7)
+        with torch.no_grad():
+            moe.router.weight.copy_(torch.empty(E, D, device=dev).normal_(0, 0.3, generator=g))
+            for e in range(moe.num_local_experts):
+                wgu, wd = _expert_weights(rank * moe.num_local_experts + e, D, FF, dev)
+                moe.experts.w_gate_up[e].copy_(wgu)
+                moe.experts.w_down[e].copy_(wd)
+        fused = FusedExpertParallel(moe, max_tokens=T)
+        results = []
+        for call in range(3):  # repeated calls reuse the same symmetric buffers
+            gx = torch.Generator(device=dev).manual_seed(100 + rank + 10 * call)
+            n = T if call != 1 else T // 2  # a smaller batch in between
+            x = torch.randn(1, n, D, generator=gx, device=dev).bfloat16()
+            with torch.no_grad():
+                results.append((fused(x), moe(x)))
+        torch.cuda.synchronize()
+        status = ops.read_status()
+        dist.barrier()  # every rank has finished its GPU work before anyone may fail and leave
+        assert status == 0
+        for got, want in results:
+            # same kernels, same row order inside every expert: the two paths must agree exactly
+            assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
+    except Exception as exc:
+        import traceback
+
+        failure = f"rank {rank}: {exc}\n{traceback.format_exc()}"
+    finally:
+        try:
+            dist.barrier()
+            dist.destroy_process_group()
+        except Exception:
+            pass
+    if failure:
+        q.put(failure)
+        raise SystemExit(1)
+
+
+def test_fused_exchange_matches_nccl_path_on_two_gpus():
+    """Dispatch by peer stores + return trip in the GEMM epilogue against the NCCL all-to-all path."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_fused_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    msgs = []
+    while not q.empty():
+        msgs.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert not msgs, "\n".join(msgs)
+    assert all(p.exitcode == 0 for p in procs)
+
+
 def test_ep_layer_two_gpus_matches_single_rank_ground_truth():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
