@@ -28,6 +28,7 @@ constexpr int kABytes = kBM * kBK * 2;        // 16 KB
 constexpr int kBBytes = kBN * kBK * 2;        // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kGemmThreads = 192;
+constexpr int kEpiStageBytes = 4 * 32 * 128;  // epilogue staging: one 32-row x 128-byte block per warp
 constexpr int kMaxExperts = 1024;
 constexpr uint32_t kSpinLimit = 1u << 24;  // probes per wait before giving up (about a second)
 
@@ -172,7 +173,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   int* abort_flag = reinterpret_cast<int*>(tmem_base_slot + 1);
-  int* mb_prefix = abort_flag + 1;  // [E + 1]
+  uint4* stage = reinterpret_cast<uint4*>(smem + kStages * kStageBytes + 256);  // 4 warps x 32 rows x 128 B
+  int* mb_prefix = reinterpret_cast<int*>(smem + kStages * kStageBytes + 256 + kEpiStageBytes);  // [E + 1]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -276,55 +278,61 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int row = quarter * 32 + lane;
       const bool valid = row < c.rows;
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
-      // destination row: the same row as in A, or wherever the row map sends it (rows are
-      // stored one per thread, so scattering them costs nothing extra)
-      int64_t out_row = c.row0 + row;
-      __nv_bfloat16* out_base = a.C;
-      if (valid && a.c_row_ptrs != nullptr) {
-        // the row lives wherever the table says, e.g. in the buffer of the GPU that owns the
-        // token: the return trip of the expert-parallel layer rides on the epilogue's stores
-        out_base = reinterpret_cast<__nv_bfloat16*>(a.c_row_ptrs[out_row]);
-        out_row = 0;
-        if (out_base == nullptr) out_base = a.C, out_row = c.row0 + row;
-      } else if (valid && a.c_row_map != nullptr) {
-        out_row = a.c_row_map[out_row];
+      // Address of this lane's output row (0 = no row): the same row as in A, the row the map
+      // names, or wherever the address table points (possibly another GPU's memory).
+      const int out_cols = a.swiglu ? 128 : kBN;
+      char* my_row = nullptr;
+      if (valid) {
+        const int64_t a_row = c.row0 + row;
+        if (a.c_row_ptrs != nullptr) my_row = reinterpret_cast<char*>(a.c_row_ptrs[a_row]);
+        if (my_row == nullptr) {
+          const int64_t out_row = (a.c_row_ptrs == nullptr && a.c_row_map != nullptr) ? a.c_row_map[a_row] : a_row;
+          if (a.C != nullptr) my_row = reinterpret_cast<char*>(a.C + out_row * a.ldc);
+        }
+        if (my_row != nullptr) my_row += static_cast<int64_t>(c.nb) * out_cols * 2;
       }
-      if (a.swiglu) {
-        __nv_bfloat16* crow = out_base + out_row * a.ldc + static_cast<int64_t>(c.nb) * 128;
+      // The accumulator arrives one row per lane. Rows are regrouped through a small
+      // swizzled staging buffer so that every store instruction writes four complete
+      // 128-byte row segments: full lines for HBM, full packets for NVLink peers.
+      uint4* stage_w = stage + (warp - 2) * (32 * 8);
 #pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld32(taddr + c0, g);
-          tmem_ld32(taddr + 128 + c0, u);
-          tmem_ld_wait();
-          if (valid) {
+      for (int c0 = 0; c0 < out_cols; c0 += 64) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8];
+        for (int h = 0; h < 2; ++h) {
+          float f[32];
+          if (a.swiglu) {
+            uint32_t g[32], u[32];
+            tmem_ld32(taddr + c0 + 32 * h, g);
+            tmem_ld32(taddr + 128 + c0 + 32 * h, u);
+            tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                f[i] = silu(__uint_as_float(g[8 * v + i])) * __uint_as_float(u[8 * v + i]);
-              *reinterpret_cast<uint4*>(crow + c0 + 8 * v) = pack16<FMOE_BF16>(f);
-            }
+            for (int i = 0; i < 32; ++i) f[i] = silu(__uint_as_float(g[i])) * __uint_as_float(u[i]);
+          } else {
+            uint32_t r[32];
+            tmem_ld32(taddr + c0 + 32 * h, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int q = 4 * h + v;  // 16-byte piece of this row's 128-byte segment
+            stage_w[lane * 8 + (q ^ (lane & 7))] = pack16<FMOE_BF16>(f + 8 * v);
           }
         }
-      } else {
-        __nv_bfloat16* crow = out_base + out_row * a.ldc + static_cast<int64_t>(c.nb) * kBN;
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(taddr + c0, r);
-          tmem_ld_wait();
-          if (valid) {
+        __syncwarp();
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * v + i]);
-              *reinterpret_cast<uint4*>(crow + c0 + 8 * v) = pack16<FMOE_BF16>(f);
-            }
+        for (int step = 0; step < 8; ++step) {
+          const int r = step * 4 + (lane >> 3);
+          const int q = lane & 7;
+          const unsigned long long rp =
+              __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_row), r);
+          if (rp != 0) {
+            const uint4 val = stage_w[r * 8 + (q ^ (r & 7))];
+            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(rp) + c0 * 2 + q * 16) = val;
           }
         }
+        __syncwarp();
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -438,10 +446,11 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   g.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
   g.status = status;
 
-  const size_t smem = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + sizeof(int) * (E + 2);
+  const size_t smem = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + kEpiStageBytes + sizeof(int) * (E + 2);
   // per device and cheap: set on every call rather than caching per device
   FMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 1024 + kStages * kStageBytes + 256 + static_cast<int>(sizeof(int)) * (kMaxExperts + 2)));
+                                 1024 + kStages * kStageBytes + 256 + kEpiStageBytes +
+                                     static_cast<int>(sizeof(int)) * (kMaxExperts + 2)));
   // upper bound of the tile count, known without reading the counts: one partial block per expert
   const int64_t max_tiles = (R / kBM + E) * g.n_blocks;
   const int grid = static_cast<int>(max_tiles < g_gemm_sms ? max_tiles : g_gemm_sms);
