@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from ctypes import c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
 
 from . import build as _build
 

@@ -229,10 +229,13 @@ static int launch_gather_sum(const Source& src, void* out, int64_t out_row_strid
   const TileCfg cfg = pick_tile(dvec, g_gather_v > 0 ? g_gather_v : 2, g_gather_threads);
   auto launch = [&](auto kernel) {
     int ctas = g_gather_ctas_per_sm;
-    if (ctas < 0) {  // auto: exactly as many CTAs as stay resident
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, kernel, cfg.threads, 0) != cudaSuccess ||
-          ctas < 1)
-        ctas = 1;
+    if (ctas < 0) {  // auto: exactly as many CTAs as stay resident (asked once per kernel and CTA size)
+      static int resident[9] = {};  // indexed by threads / 32; one array per kernel instantiation
+      int& slot = resident[cfg.threads / 32];
+      if (slot == 0 &&
+          (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&slot, kernel, cfg.threads, 0) != cudaSuccess || slot < 1))
+        slot = 1;
+      ctas = slot;
     }
     const int g = static_cast<int>(clamp_grid(T * cfg.tiles, ctas));
     kernel<<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);

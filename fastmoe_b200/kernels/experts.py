@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import torch
 
-from .. import _lib
 from . import ops
 from .ops import _require_cuda, _status_word, _stream_ptr
 

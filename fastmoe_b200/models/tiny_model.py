@@ -218,7 +218,21 @@ class MoEFeedForward(nn.Module):
             return out.view(B, T, D)
         raise NotImplementedError
 
+    def enable_fused_exchange(self, max_tokens, capacity_factor=2.0):
+        """With several ranks and SwiGLU experts: lets gradient-free bf16 forwards of up to
+        `max_tokens` tokens run with the exchange fused into the permute kernel and the GEMM
+        epilogue (peer stores over NVLink, no all-to-all, no host synchronisation; see
+        fastmoe_b200/ep_fused.py). Collective: every rank of the group must call it."""
+        from ..ep_fused import FusedExpertParallel
+
+        self._fused_exchange = FusedExpertParallel(self, max_tokens, capacity_factor, self.group)
+        return self
+
     def forward(self, x):
+        fused = getattr(self, "_fused_exchange", None)
+        if (fused is not None and not torch.is_grad_enabled() and x.dtype == torch.bfloat16
+                and x.shape[0] * x.shape[1] * self.top_k <= fused.max_rows):  # fmt: skip
+            return fused(x)
         permuted, send_rank_counts, send_exp_counts, rev_idx, weights, shape = self.gate_and_sort(x)
         recv, recv_splits, send_splits, tokens_per_expert = self.dispatch_exchange(
             permuted, send_rank_counts, send_exp_counts

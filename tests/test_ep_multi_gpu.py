@@ -126,6 +126,13 @@ def _fused_worker(rank, world, port, q):
             with torch.no_grad():
                 results.append((fused(x), moe(x)))
         torch.cuda.synchronize()
+        # the module-level switch routes gradient-free forwards through the same fused path
+        moe.enable_fused_exchange(max_tokens=T)
+        with torch.no_grad():
+            via_module = moe(x)
+        results.append((via_module, results[-1][1]))
+        assert moe(x.requires_grad_(True)).requires_grad  # with gradients: the NCCL path, as before
+        torch.cuda.synchronize()
         status = ops.read_status()
         dist.barrier()  # every rank has finished its GPU work before anyone may fail and leave
         assert status == 0
