@@ -71,7 +71,7 @@ GEMM = {
 # DRAM bytes (read + write) of one gather launch on the default workload: the ncu
 # capture of the quarter-size case (profiles/combine_gather_cfg2.md) scaled by its
 # 4x tokens; traffic grows in proportion to tokens.
-NCU_TRAFFIC_BYTES = {DEFAULT_WORKLOAD: 4 * (537_091_584 + 45_902_592)}
+NCU_TRAFFIC_BYTES = {DEFAULT_WORKLOAD: 4 * (537_092_352 + 45_110_528)}
 
 FALLBACK_HBM_GBS = 6650.0
 
