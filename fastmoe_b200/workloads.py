@@ -76,9 +76,23 @@ class CombineWorkload:
 
 
 def make_combine_workload(T, D, E, K, dtype=torch.bfloat16, routing="softmax", seed=0, device="cuda"):
-    """E disjoint expert output matrices with N(0,1) rows plus expert-major routing."""
-    topk_idx, topk_w = ROUTINGS[routing](T, E, K, seed)
-    reverse_map, sorted_w, counts = sort_routing(topk_idx, topk_w, E)
+    """E disjoint expert output matrices with N(0,1) rows plus expert-major routing.
+
+    routing="random_targets" reproduces the reference microbenchmark's inputs instead
+    (src/fastmoe/benchmarks/run_on_cloud.py:207-214): T*K rows split evenly over the experts,
+    every row aimed at a uniformly random token (duplicates and untouched tokens included),
+    uniform(0,1) weights."""
+    if routing == "random_targets":
+        g = torch.Generator().manual_seed(seed)
+        n = T * K
+        reverse_map = torch.randint(0, T, (n,), generator=g)
+        sorted_w = torch.rand(n, generator=g)
+        counts = torch.tensor([len(c) for c in torch.arange(n).chunk(E)] + [0] * max(0, E - n), dtype=torch.int64)[:E]
+        topk_idx = torch.zeros(0, K, dtype=torch.int64)
+        topk_w = torch.zeros(0, K)
+    else:
+        topk_idx, topk_w = ROUTINGS[routing](T, E, K, seed)
+        reverse_map, sorted_w, counts = sort_routing(topk_idx, topk_w, E)
     device = torch.device(device)
     gen = torch.Generator(device=device).manual_seed(seed + 1)
     experts, spacers = [], []

@@ -1,0 +1,28 @@
+"""bench.py's reference arm runs without a GPU (it times the CPU port of the reference's path):
+here on a small workload, checking the JSON line the driver parses."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_reference_arm_prints_one_json_line_with_the_contract_keys():
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "2", "--warmup", "1",
+         "--workload", "combine_small_bf16_T1024_D4096_E64_top8"],
+        capture_output=True, text=True, timeout=300, env={"CUDA_VISIBLE_DEVICES": "", "PATH": "/usr/bin:/bin"},
+    )  # fmt: skip
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "combine_hbm_gbs" and d["unit"] == "GB/s"
+    for key in ("value", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "dtype",
+                "data", "config", "cpu_baseline", "e2e"):  # fmt: skip
+        assert key in d, key
+    assert d["steps"] == 2 and d["value"] > 0 and d["config"]["workload"].startswith("combine_small")
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"]
