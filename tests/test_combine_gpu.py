@@ -227,3 +227,29 @@ def test_medium_workload_all_dtypes(routing):
             out = ops.grouped_weighted_scatter_add(wl.experts, wl.indices, wl.weights, (wl.T, wl.D))
             err = assert_close(out, ref, dtype, f"{routing}/{mode}/{dtype}")
             assert err <= REL_TOL[dtype]
+
+
+def test_cuda_graph_capture_and_replay_like_the_reference_benchmark():
+    """The reference's microbenchmark captures `grouped_weighted_scatter_add(..., out=, metadata=)`
+    in a CUDA graph and replays it after zeroing `out` (run_on_cloud.py:64-91). The same flow must
+    work here, in both combine modes, and give the oracle's result on every replay."""
+    wl = make_combine_workload(T=256, D=2048, E=32, K=4, dtype=torch.float32, seed=9)
+    shape = (wl.T, wl.D)
+    ref = oracle_combine(wl.experts, wl.indices, wl.weights, wl.T)
+    for mode in MODES:
+        ops.set_combine_mode(mode)
+        out_static = torch.zeros(shape, device=DEV)
+        metadata = ops.prepare_grouped_metadata(wl.experts, out_static.device)
+        ops.grouped_weighted_scatter_add(wl.experts, wl.indices, wl.weights, shape, out=out_static, metadata=metadata)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        out_static.zero_()
+        with torch.cuda.graph(graph):
+            ops.grouped_weighted_scatter_add(wl.experts, wl.indices, wl.weights, shape, out=out_static, metadata=metadata)
+        for _ in range(3):
+            out_static.zero_()
+            graph.replay()
+        torch.cuda.synchronize()
+        assert_close(out_static, ref, torch.float32, f"graph replay / {mode}")
+        if mode == "gather":
+            assert np.array_equal(to_np(out_static), ref)
