@@ -610,6 +610,25 @@ def run_gemm(args, rank, world, local_rank):
     each = [a.elapsed_time(b) for a, b in pairs]
     gate_up_ms, down_ms = statistics.mean(each[0::2]), statistics.mean(each[1::2])
     assert ops.read_status(dev) == 0 and bool(torch.isfinite(y.float()).all())
+
+    # forward + backward (data and weight gradients on the same kernels), fewer steps
+    xg, wgu_g, wd_g = x.clone().requires_grad_(True), wgu.requires_grad_(True), wd.requires_grad_(True)
+    gy = torch.randn(R, D, generator=gen, device=dev, dtype=torch.bfloat16)
+
+    def train_step():
+        xg.grad = wgu_g.grad = wd_g.grad = None
+        experts.grouped_swiglu_ffn(xg, wgu_g, wd_g, off, cnt, covers_all_rows=True).backward(gy)
+
+    fb_steps = max(2, min(args.steps, 5))
+    train_step()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(fb_steps):
+        train_step()
+    end.record()
+    torch.cuda.synchronize()
+    fb_ms = start.elapsed_time(end) / fb_steps
+    assert ops.read_status(dev) == 0
     if rank != 0:
         return
     peak, kind = measured_tflops()
@@ -624,7 +643,10 @@ def run_gemm(args, rank, world, local_rank):
         "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (gate/up + down)", "achieved": achieved,
                      "peak": peak, "peak_kind": kind, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                      "gate_up_ms": gate_up_ms, "gate_up_tflops": 4 * R * D * FF / gate_up_ms / 1e9,
-                     "down_ms": down_ms, "down_tflops": 2 * R * D * FF / down_ms / 1e9},
+                     "down_ms": down_ms, "down_tflops": 2 * R * D * FF / down_ms / 1e9,
+                     "fwd_bwd_ms": fb_ms, "fwd_bwd_tflops": 4 * flops / fb_ms / 1e9,
+                     "fwd_bwd_note": "3x the forward products plus the gate/up recomputation (4x flops), "
+                                     "SwiGLU derivative as elementwise torch code in between"},
         "clocks": clocks.summary(),
     }  # fmt: skip
     print(json.dumps(line), flush=True)

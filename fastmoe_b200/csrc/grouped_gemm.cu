@@ -46,6 +46,7 @@ struct GemmArgs {
   int w_rows_per_expert;   // rows of the weight tensor per expert (N, or 2*ff for SwiGLU)
   int up_row_offset;       // SwiGLU: row of the first "up" weight inside an expert (= ff), else 128
   int swiglu;
+  int w_transposed;        // 1: data gradient, C = A x W (W is [E, K_red, N_out]: the reduction runs over W's rows)
   int skip_loads;  // test hook: the producer issues nothing, so every consumer wait runs out
   uint32_t spin_limit;
   int32_t* status;
@@ -128,8 +129,21 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
   d |= static_cast<uint64_t>(2) << 61;                       // 128-byte swizzle
   return d;
 }
+// The same for an operand whose MN dimension is the contiguous one (a row-major [K, N] weight
+// used as B): 64-element (128-byte) pieces of the MN dimension are separate TMA boxes
+// `mn_piece_bytes` apart, and inside a box every 8 reduction rows form a 1024-byte group.
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t saddr, uint32_t mn_piece_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr >> 4) & 0x3fff);
+  d |= static_cast<uint64_t>((mn_piece_bytes >> 4) & 0x3fff) << 16;  // leading byte offset: next MN piece
+  d |= static_cast<uint64_t>((1024 >> 4) & 0x3fff) << 32;            // stride byte offset: next 8 reduction rows
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
 // Instruction descriptor: D fp32, A and B bf16, both K-major, M=128, N=256.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+constexpr uint32_t kIdescBMn = kIdesc | (1u << 16);  // B with the N dimension contiguous
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
@@ -161,7 +175,7 @@ __device__ __forceinline__ TileCoord locate_tile(int tile, const int* mb_prefix,
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                        const GemmArgs a) {
+                        const GemmArgs a) {  // map_w: box 64 x 128 rows (forward) or 64 x 64 rows (w_transposed)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -234,8 +248,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
         mbar_expect_tx(&full[stage], kStageBytes);
         tma_load_2d(smem_a + stage * kABytes, &map_a, kb * kBK, static_cast<int>(c.row0), &full[stage]);
-        tma_load_2d(smem_b + stage * kBBytes, &map_w, kb * kBK, w_row0, &full[stage]);
-        tma_load_2d(smem_b + stage * kBBytes + kBBytes / 2, &map_w, kb * kBK, w_row1, &full[stage]);
+        if (a.w_transposed) {
+          // W[e] is [K_red, N_out] row-major: four boxes of 64 output columns x 64 reduction rows
+          const int red_row = c.expert * a.w_rows_per_expert + kb * kBK;
+#pragma unroll
+          for (int piece = 0; piece < 4; ++piece)
+            tma_load_2d(smem_b + stage * kBBytes + piece * (kBBytes / 4), &map_w, c.nb * kBN + piece * 64, red_row,
+                        &full[stage]);
+        } else {
+          tma_load_2d(smem_b + stage * kBBytes, &map_w, kb * kBK, w_row0, &full[stage]);
+          tma_load_2d(smem_b + stage * kBBytes + kBBytes / 2, &map_w, kb * kBK, w_row1, &full[stage]);
+        }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
@@ -254,11 +277,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!mbar_wait(&full[stage], phase, abort_flag, a.spin_limit)) goto timed_out;
         tcgen05_fence_after();
         const uint64_t da = smem_desc(smem_u32(smem_a + stage * kABytes));
-        const uint64_t db = smem_desc(smem_u32(smem_b + stage * kBBytes));
+        if (a.w_transposed) {
+          const uint64_t db = smem_desc_mn(smem_u32(smem_b + stage * kBBytes), kBBytes / 4);
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) {
-          // 16 bf16 = 32 bytes along K inside the swizzle atom: +2 in the encoded address
-          umma_bf16(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // A: +32 bytes along K; B: 16 reduction rows of 128 bytes further = +2048 bytes
+            umma_bf16(tmem_d, da + 2 * k, db + 128 * k, kIdescBMn, (kb | k) != 0 ? 1u : 0u);
+          }
+        } else {
+          const uint64_t db = smem_desc(smem_u32(smem_b + stage * kBBytes));
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // 16 bf16 = 32 bytes along K inside the swizzle atom: +2 in the encoded address
+            umma_bf16(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(&empty[stage]);  // frees the stage when these MMAs have read it
         if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -355,6 +387,211 @@ done:
   }
 }
 
+// ---- weight gradient ------------------------------------------------------------------------
+// grad_w[e][n, k] = sum over the rows m of expert e of grad_c[m, n] * a[m, k].
+// The reduction runs over the ROWS of both operands, so both are used with their
+// contiguous dimension as the MN dimension: 64-wide TMA boxes of 64 rows each (two for the
+// 128 n of a tile, four for its 256 k). An expert's last 64-row chunk may reach into the
+// next expert's rows: the MMA warp zeroes those rows of the grad_c tile in shared memory
+// before the MMAs read it (rows past the end of the tensor are zero-filled by TMA). Tiles
+// are (expert, n block, k block) with a fixed count per expert, so no tile table is needed;
+// an expert without rows gets zeros straight from the epilogue.
+struct WgradArgs {
+  const int64_t* offsets;
+  const int64_t* counts;
+  __nv_bfloat16* grad_w;  // [E, N, K]
+  int64_t N, K;
+  int E, n_blocks, k_blocks;  // tiles per expert: N/128 x K/256
+  int skip_loads;
+  uint32_t spin_limit;
+  int32_t* status;
+};
+
+constexpr uint32_t kIdescAllMn = kIdesc | (1u << 15) | (1u << 16);  // A and B with MN contiguous
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    grouped_wgrad_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_a,
+                         const WgradArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;                       // grad_c tile: 2 boxes x 8 KB per stage
+  uint8_t* smem_b = smem + kStages * kABytes;   // a tile: 4 boxes x 8 KB per stage
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty = full + kStages;
+  uint64_t* tmem_full = empty + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  int* abort_flag = reinterpret_cast<int*>(tmem_base_slot + 1);
+  uint4* stage_buf = reinterpret_cast<uint4*>(smem + kStages * kStageBytes + 256);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_base_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int tiles_per_expert = a.n_blocks * a.k_blocks;
+  const int total_tiles = a.E * tiles_per_expert;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer ---------------------------------------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !a.skip_loads; tile += gridDim.x) {
+      const int e = tile / tiles_per_expert;
+      const int local = tile - e * tiles_per_expert;
+      const int nb = local / a.k_blocks, kbk = local - nb * a.k_blocks;
+      const int64_t row0 = a.offsets[e];
+      const int chunks = static_cast<int>((a.counts[e] + kBK - 1) / kBK);
+      for (int kb = 0; kb < chunks; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
+        mbar_expect_tx(&full[stage], kStageBytes);
+        const int row = static_cast<int>(row0) + kb * kBK;
+#pragma unroll
+        for (int piece = 0; piece < 2; ++piece)
+          tma_load_2d(smem_a + stage * kABytes + piece * (kABytes / 2), &map_g, nb * kBM + piece * 64, row,
+                      &full[stage]);
+#pragma unroll
+        for (int piece = 0; piece < 4; ++piece)
+          tma_load_2d(smem_b + stage * kBBytes + piece * (kBBytes / 4), &map_a, kbk * kBN + piece * 64, row,
+                      &full[stage]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA warp: all lanes mask a ragged chunk, lane 0 issues the MMAs ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int e = tile / tiles_per_expert;
+      const int64_t rows = a.counts[e];
+      const int chunks = static_cast<int>((rows + kBK - 1) / kBK);
+      if (chunks == 0) continue;  // the epilogue writes zeros for this tile on its own
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
+      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
+      tcgen05_fence_after();
+      const uint32_t tmem_d = tmem_base + acc * kBN;
+      for (int kb = 0; kb < chunks; ++kb) {
+        if (!mbar_wait(&full[stage], phase, abort_flag, a.spin_limit)) goto timed_out;
+        const int valid = static_cast<int>(rows - static_cast<int64_t>(kb) * kBK);
+        if (valid < kBK) {
+          // rows valid..63 of this chunk belong to the next expert: clear them in the grad_c
+          // tile (each reduction row is one 128-byte line in each of the two boxes)
+          uint4* tile_g = reinterpret_cast<uint4*>(smem_a + stage * kABytes);
+          const int lines = (kBK - valid) * 2;
+          for (int i = lane; i < lines * 8; i += 32) {
+            const int line = i >> 3, piece = line & 1, r = valid + (line >> 1);
+            tile_g[piece * (kABytes / 2 / 16) + r * 8 + (i & 7)] = make_uint4(0, 0, 0, 0);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor core reads
+        }
+        __syncwarp();
+        tcgen05_fence_after();
+        if (lane == 0) {
+          const uint64_t da = smem_desc_mn(smem_u32(smem_a + stage * kABytes), kABytes / 2);
+          const uint64_t db = smem_desc_mn(smem_u32(smem_b + stage * kBBytes), kBBytes / 4);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k)
+            umma_bf16(tmem_d, da + 128 * k, db + 128 * k, kIdescAllMn, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(&empty[stage]);
+          if (kb == chunks - 1) umma_commit(&tmem_full[acc]);
+        }
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue -------------------------------------------------------------------
+    const int quarter = warp & 3;
+    uint4* stage_w = stage_buf + (warp - 2) * (32 * 8);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int e = tile / tiles_per_expert;
+      const int local = tile - e * tiles_per_expert;
+      const int nb = local / a.k_blocks, kbk = local - nb * a.k_blocks;
+      const bool empty_expert = a.counts[e] <= 0;
+      const int row = quarter * 32 + lane;
+      char* my_row = reinterpret_cast<char*>(a.grad_w + (static_cast<int64_t>(e) * a.N + nb * kBM + row) * a.K +
+                                             static_cast<int64_t>(kbk) * kBN);
+      int acc = 0;
+      if (!empty_expert) {
+        acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
+        if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, a.spin_limit)) goto timed_out;
+        tcgen05_fence_after();
+      }
+      const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBN; c0 += 64) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float f[32];
+          if (empty_expert) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = 0.f;
+          } else {
+            uint32_t r[32];
+            tmem_ld32(taddr + c0 + 32 * h, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) stage_w[lane * 8 + ((4 * h + v) ^ (lane & 7))] = pack16<FMOE_BF16>(f + 8 * v);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int step = 0; step < 8; ++step) {
+          const int r = step * 4 + (lane >> 3);
+          const int q = lane & 7;
+          const unsigned long long rp = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_row), r);
+          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(rp) + c0 * 2 + q * 16) = stage_w[r * 8 + (q ^ (r & 7))];
+        }
+        __syncwarp();
+      }
+      if (!empty_expert) {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      }
+    }
+  }
+  goto done;
+
+timed_out:
+  *abort_flag = 1;
+  if (a.status != nullptr) atomicOr(a.status, FMOE_STATUS_WAIT_TIMEOUT);
+
+done:
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------
 // SMs the persistent grid may occupy (fmoe_tune "gemm_sms"). Leaving a few SMs free lets
 // NCCL's copy kernels run beside the GEMM instead of waiting for its CTAs to retire.
@@ -380,13 +617,14 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// 2-D bf16 row-major tensor [rows, cols], box = 64 columns x 128 rows, 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, const char* what) {
+// 2-D bf16 row-major tensor [rows, cols], box = 64 columns x box_rows rows, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, const char* what,
+                    int box_rows = 128) {
   EncodeTiledFn fn = encode_tiled_fn();
   FMOE_REQUIRE(fn != nullptr, FMOE_ERR_DEVICE, "fmoe_grouped_gemm: cuTensorMapEncodeTiled is not available");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  const cuuint32_t box[2] = {kBK, 128};
+  const cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -442,6 +680,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   g.w_rows_per_expert = static_cast<int>(N);
   g.up_row_offset = static_cast<int>(swiglu ? N / 2 : 128);
   g.swiglu = swiglu ? 1 : 0;
+  g.w_transposed = 0;
   g.skip_loads = g_gemm_skip_loads;
   g.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
   g.status = status;
@@ -456,4 +695,96 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   const int grid = static_cast<int>(max_tiles < g_gemm_sms ? max_tiles : g_gemm_sms);
   grouped_gemm_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(map_a, map_w, g);
   return check_launch("grouped_gemm_kernel");
+}
+
+extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* grad_a, const int64_t* offsets,
+                                       const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
+                                       int32_t* status, void* stream) {
+  FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm_dgrad: bad sizes");
+  FMOE_REQUIRE(E <= kMaxExperts, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm_dgrad: supports E <= %d", kMaxExperts);
+  FMOE_REQUIRE(N % kBK == 0 && K % kBN == 0, FMOE_ERR_UNSUPPORTED,
+               "fmoe_grouped_gemm_dgrad: N=%lld must be a multiple of %d and K=%lld of %d", (long long)N, kBK,
+               (long long)K, kBN);
+  FMOE_REQUIRE(R < (1ll << 31) && E * N < (1ll << 31), FMOE_ERR_UNSUPPORTED,
+               "fmoe_grouped_gemm_dgrad: R and E*N must fit in int32");
+  if (E == 0 || R == 0) return FMOE_OK;
+  FMOE_REQUIRE(grad_c && w && grad_a && offsets && counts, FMOE_ERR_ARG,
+               "fmoe_grouped_gemm_dgrad: null pointer argument");
+  FMOE_REQUIRE(aligned_to(grad_c, 16) && aligned_to(w, 16) && aligned_to(grad_a, 16), FMOE_ERR_ARG,
+               "fmoe_grouped_gemm_dgrad: grad_c, w and grad_a must be 16-byte aligned");
+  CUtensorMap map_a, map_w;
+  int rc = make_map(&map_a, grad_c, R, N, "grad_c");
+  if (rc != 0) return rc;
+  rc = make_map(&map_w, w, E * N, K, "W (transposed use)", 64);
+  if (rc != 0) return rc;
+  GemmArgs g;
+  g.offsets = offsets;
+  g.counts = counts;
+  g.c_row_map = nullptr;
+  g.c_row_ptrs = nullptr;
+  g.C = static_cast<__nv_bfloat16*>(grad_a);
+  g.ldc = K;
+  g.R = R;
+  g.E = static_cast<int>(E);
+  g.n_blocks = static_cast<int>(K / kBN);   // output columns are W's columns
+  g.k_blocks = static_cast<int>(N / kBK);   // the reduction runs over W's rows
+  g.w_rows_per_expert = static_cast<int>(N);
+  g.up_row_offset = 0;
+  g.swiglu = 0;
+  g.w_transposed = 1;
+  g.skip_loads = g_gemm_skip_loads;
+  g.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
+  g.status = status;
+  const size_t smem = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + kEpiStageBytes + sizeof(int) * (E + 2);
+  FMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 1024 + kStages * kStageBytes + 256 + kEpiStageBytes +
+                                     static_cast<int>(sizeof(int)) * (kMaxExperts + 2)));
+  const int64_t max_tiles = (R / kBM + E) * g.n_blocks;
+  const int grid = static_cast<int>(max_tiles < g_gemm_sms ? max_tiles : g_gemm_sms);
+  grouped_gemm_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(map_a, map_w, g);
+  return check_launch("grouped_gemm_kernel (dgrad)");
+}
+
+extern "C" int fmoe_grouped_gemm_wgrad(const void* grad_c, const void* a, void* grad_w, const int64_t* offsets,
+                                       const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
+                                       int32_t* status, void* stream) {
+  FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm_wgrad: bad sizes");
+  FMOE_REQUIRE(N % kBM == 0 && K % kBN == 0, FMOE_ERR_UNSUPPORTED,
+               "fmoe_grouped_gemm_wgrad: N=%lld must be a multiple of %d and K=%lld of %d", (long long)N, kBM,
+               (long long)K, kBN);
+  FMOE_REQUIRE(R < (1ll << 31) && E * (N / kBM) * (K / kBN) < (1ll << 31), FMOE_ERR_UNSUPPORTED,
+               "fmoe_grouped_gemm_wgrad: sizes must fit in int32");
+  if (E == 0) return FMOE_OK;
+  FMOE_REQUIRE(grad_w && offsets && counts && (R == 0 || (grad_c && a)), FMOE_ERR_ARG,
+               "fmoe_grouped_gemm_wgrad: null pointer argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (R == 0) {  // no rows at all: every expert's gradient is zero
+    FMOE_CUDA(cudaMemsetAsync(grad_w, 0, static_cast<size_t>(E) * N * K * 2, s));
+    return FMOE_OK;
+  }
+  FMOE_REQUIRE(aligned_to(grad_c, 16) && aligned_to(a, 16) && aligned_to(grad_w, 16), FMOE_ERR_ARG,
+               "fmoe_grouped_gemm_wgrad: grad_c, a and grad_w must be 16-byte aligned");
+  CUtensorMap map_g, map_a;
+  int rc = make_map(&map_g, grad_c, R, N, "grad_c (row reduction)", 64);
+  if (rc != 0) return rc;
+  rc = make_map(&map_a, a, R, K, "a (row reduction)", 64);
+  if (rc != 0) return rc;
+  WgradArgs g;
+  g.offsets = offsets;
+  g.counts = counts;
+  g.grad_w = static_cast<__nv_bfloat16*>(grad_w);
+  g.N = N;
+  g.K = K;
+  g.E = static_cast<int>(E);
+  g.n_blocks = static_cast<int>(N / kBM);
+  g.k_blocks = static_cast<int>(K / kBN);
+  g.skip_loads = g_gemm_skip_loads;
+  g.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
+  g.status = status;
+  const int smem = 1024 + kStages * kStageBytes + 256 + kEpiStageBytes;
+  FMOE_CUDA(cudaFuncSetAttribute(grouped_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const int64_t tiles = E * g.n_blocks * g.k_blocks;
+  const int grid = static_cast<int>(tiles < g_gemm_sms ? tiles : g_gemm_sms);
+  grouped_wgrad_kernel<<<grid, kGemmThreads, smem, s>>>(map_g, map_a, g);
+  return check_launch("grouped_wgrad_kernel");
 }

@@ -6,9 +6,11 @@ memory, and `grouped_swiglu_ffn` chains two of them into down(silu(gate(x)) * up
 They replace the Python loop over `self.experts` in `MoEFeedForward.compute_experts` of
 polkadot21/fastmoe (src/fastmoe/models/tiny_model.py:282-294).
 
-Forward runs on the hand-written kernel (`csrc/grouped_gemm.cu`). The backward pass is
-composed from per-expert matrix products through torch (library GEMMs) and needs the
-counts on the host.
+Forward, data gradient and weight gradient all run on the hand-written tcgen05 kernels
+(`csrc/grouped_gemm.cu`) with the per-expert row ranges read from device memory; the
+SwiGLU derivative between them is elementwise torch code on recomputed pre-activations.
+Shapes the kernels do not tile (N or K not a multiple of 64/128/256) fall back to
+per-expert library products.
 """
 
 from __future__ import annotations
@@ -66,24 +68,67 @@ class _GroupedGemm(torch.autograd.Function):
         a, w, offsets, counts, row_map = ctx.saved_tensors
         if row_map is not None:
             grad_c = grad_c.index_select(0, row_map)  # back to the row order of `a`
-        offs, cnts = offsets.tolist(), counts.tolist()
-        grad_a = torch.zeros_like(a)
-        grad_w = torch.zeros_like(w)
-        ff = w.shape[1] // 2
-        for e, (o, n) in enumerate(zip(offs, cnts)):
-            if n == 0:
-                continue
-            x, g = a[o : o + n], grad_c[o : o + n]
-            if ctx.swiglu:
-                h = (x @ w[e].t()).float()
-                gate, up = h[:, :ff], h[:, ff:]
-                sig = torch.sigmoid(gate)
-                d_gate = g.float() * up * sig * (1 + gate * (1 - sig))
-                d_up = g.float() * gate * sig
-                g = torch.cat([d_gate, d_up], dim=1).to(a.dtype)
-            grad_a[o : o + n] = g @ w[e]
-            grad_w[e] = g.t() @ x
+        grad_c = grad_c.contiguous()
+        if ctx.swiglu:
+            # recompute the pre-activations with the plain kernel, then the SwiGLU derivative
+            ff = w.shape[1] // 2
+            h = _launch(a, w, offsets, counts, False, covers_all_rows=False).float()
+            gate, up = h[:, :ff], h[:, ff:]
+            sig = torch.sigmoid(gate)
+            g32 = grad_c.float()
+            grad_c = torch.cat([g32 * up * sig * (1 + gate * (1 - sig)), g32 * gate * sig], dim=1).to(a.dtype)
+            del h, gate, up, sig, g32
+        need_a, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        grad_a = _dgrad(grad_c, w, offsets, counts) if need_a else None
+        grad_w = _wgrad(grad_c, a, w.shape, offsets, counts) if need_w else None
         return grad_a, grad_w, None, None, None, None, None
+
+
+def _dgrad(grad_c, w, offsets, counts):
+    """grad_a[rows of e] = grad_c[rows of e] @ w[e] on the tensor cores; rows owned by no
+    expert get zero."""
+    R, N = grad_c.shape
+    E, _, K = w.shape
+    if N % 64 or K % 256:
+        return _dgrad_library(grad_c, w, offsets, counts)
+    grad_a = torch.zeros(R, K, dtype=torch.bfloat16, device=grad_c.device)
+    ops._call(
+        "fmoe_grouped_gemm_dgrad", 1, grad_c.data_ptr(), w.contiguous().data_ptr(), grad_a.data_ptr(),
+        offsets.data_ptr(), counts.data_ptr(), E, R, N, K, _status_word(grad_c.device).data_ptr(),
+        _stream_ptr(grad_c.device),
+    )  # fmt: skip
+    return grad_a
+
+
+def _wgrad(grad_c, a, w_shape, offsets, counts):
+    """grad_w[e] = grad_c[rows of e].T @ a[rows of e] on the tensor cores."""
+    E, N, K = w_shape
+    R = a.shape[0]
+    if N % 128 or K % 256:
+        return _wgrad_library(grad_c, a, w_shape, offsets, counts)
+    grad_w = torch.empty(E, N, K, dtype=torch.bfloat16, device=a.device)
+    ops._call(
+        "fmoe_grouped_gemm_wgrad", 1, grad_c.data_ptr(), a.contiguous().data_ptr(), grad_w.data_ptr(),
+        offsets.data_ptr(), counts.data_ptr(), E, R, N, K, _status_word(a.device).data_ptr(), _stream_ptr(a.device),
+    )  # fmt: skip
+    return grad_w
+
+
+def _dgrad_library(grad_c, w, offsets, counts):
+    """Shapes the kernels do not tile: per-expert library products (needs the counts on the host)."""
+    grad_a = torch.zeros(grad_c.shape[0], w.shape[2], dtype=grad_c.dtype, device=grad_c.device)
+    for e, (o, n) in enumerate(zip(offsets.tolist(), counts.tolist())):
+        if n:
+            grad_a[o : o + n] = grad_c[o : o + n] @ w[e]
+    return grad_a
+
+
+def _wgrad_library(grad_c, a, w_shape, offsets, counts):
+    grad_w = torch.zeros(w_shape, dtype=a.dtype, device=a.device)
+    for e, (o, n) in enumerate(zip(offsets.tolist(), counts.tolist())):
+        if n:
+            grad_w[e] = grad_c[o : o + n].t() @ a[o : o + n]
+    return grad_w
 
 
 def grouped_gemm(a, w, offsets, counts, swiglu=False, row_map=None, covers_all_rows=False):

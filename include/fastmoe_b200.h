@@ -262,6 +262,29 @@ int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offs
                       int64_t E, int64_t R, int64_t N, int64_t K, int swiglu, int32_t* status,
                       void* stream);
 
+/*
+ * Data gradient of the plain grouped GEMM: grad_a[rows of e, :K] = grad_c[rows of e, :N] x W[e]
+ * (W[e] is [N, K], read as it lies in memory: its N rows are the reduction dimension and
+ * its K columns the output columns, so no transposed copy of the weights is needed). Same
+ * kernel, same ragged-row handling and limits as fmoe_grouped_gemm; N must be a multiple of
+ * 64 and K of 256. Stands for `g @ w[e]` per expert in the autograd backward of
+ * MoEFeedForward.compute_experts (src/fastmoe/models/tiny_model.py:282-294).
+ */
+int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* grad_a, const int64_t* offsets,
+                            const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
+                            int32_t* status, void* stream);
+
+/*
+ * Weight gradient of the grouped GEMM: grad_w[e] = grad_c[rows of e]^T x a[rows of e], bf16
+ * [E, N, K] with fp32 accumulation; experts without rows get zeros. The reduction runs over
+ * the expert's rows (ragged; the counts stay on the device). N must be a multiple of 128
+ * and K of 256. Stands for `g.t() @ x` per expert in the autograd backward of
+ * MoEFeedForward.compute_experts (src/fastmoe/models/tiny_model.py:282-294).
+ */
+int fmoe_grouped_gemm_wgrad(const void* grad_c, const void* a, void* grad_w, const int64_t* offsets,
+                            const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
+                            int32_t* status, void* stream);
+
 /* ---- host-buffer call -------------------------------------------------------- */
 /*
  * The whole combine for a caller that holds HOST memory: copies the E expert

@@ -135,3 +135,30 @@ def test_bounded_waits_give_up_and_report_instead_of_hanging():
     assert ops.read_status() == 0
     ref = _reference(a, w, [300, 100], False)
     assert float((c.float() - ref).abs().max() / ref.abs().max()) <= 1e-2
+
+
+@pytest.mark.parametrize("counts,K,N,swiglu", [
+    ([128], 256, 256, False),
+    ([200, 0, 5, 300], 512, 512, False),
+    ([200, 0, 5, 300], 512, 512, True),
+    ([700, 33, 64], 768, 1024, True),
+])  # fmt: skip
+def test_backward_on_tensor_cores_matches_fp32_autograd(counts, K, N, swiglu):
+    """Data and weight gradients (tcgen05 kernels with the contiguous dimension as MN, ragged
+    row reduction masked in shared memory) against fp32 autograd of the same products."""
+    a, w, off, cnt = _case(counts, K, N, swiglu, seed=21)
+    a.requires_grad_(True)
+    w.requires_grad_(True)
+    c = experts.grouped_gemm(a, w, off, cnt, swiglu=swiglu)
+    gen = torch.Generator(device=DEV).manual_seed(22)
+    g = torch.randn(c.shape, generator=gen, device=DEV).bfloat16()
+    c.backward(g)
+    torch.cuda.synchronize()
+    assert ops.read_status() == 0
+    a32 = a.detach().float().requires_grad_(True)
+    w32 = w.detach().float().requires_grad_(True)
+    _reference(a32, w32, counts, swiglu).backward(g.float())
+    for got, want, what in ((a.grad, a32.grad, "grad_a"), (w.grad, w32.grad, "grad_w")):
+        err = float((got.float() - want).abs().max() / want.abs().max())
+        assert err <= REL_TOL[torch.bfloat16], (what, err)
+    assert float(w.grad[1].abs().max()) == 0.0 if counts[1:2] == [0] else True  # an expert without rows
