@@ -620,6 +620,9 @@ static EncodeTiledFn encode_tiled_fn() {
 // 2-D bf16 row-major tensor [rows, cols], box = 64 columns x box_rows rows, 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, const char* what,
                     int box_rows = 128) {
+  // The encoder is a driver call and wants a current context. A thread that has not yet made
+  // a runtime call of this library (an autograd worker, say) may have none bound: bind it.
+  FMOE_CUDA(cudaFree(nullptr));
   EncodeTiledFn fn = encode_tiled_fn();
   FMOE_REQUIRE(fn != nullptr, FMOE_ERR_DEVICE, "fmoe_grouped_gemm: cuTensorMapEncodeTiled is not available");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};

@@ -8,7 +8,7 @@ polkadot21/fastmoe (src/fastmoe/models/tiny_model.py:282-294).
 
 Forward, data gradient and weight gradient all run on the hand-written tcgen05 kernels
 (`csrc/grouped_gemm.cu`) with the per-expert row ranges read from device memory; the
-SwiGLU derivative between them is elementwise torch code on recomputed pre-activations.
+SwiGLU derivative between them is one streaming kernel over recomputed pre-activations.
 Shapes the kernels do not tile (N or K not a multiple of 64/128/256) fall back to
 per-expert library products.
 """
@@ -60,7 +60,7 @@ class _GroupedGemm(torch.autograd.Function):
         if row_map is not None and (row_map.dtype != torch.int64 or row_map.numel() != a.shape[0]):
             raise ValueError("row_map must be an int64 device tensor with one entry per row of a")
         ctx.save_for_backward(a, w, offsets, counts, row_map)
-        ctx.swiglu = swiglu
+        ctx.swiglu, ctx.covers_all_rows = swiglu, covers_all_rows
         return _launch(a, w, offsets, counts, swiglu, row_map, covers_all_rows)
 
     @staticmethod
@@ -72,26 +72,27 @@ class _GroupedGemm(torch.autograd.Function):
         if ctx.swiglu:
             # recompute the pre-activations with the plain kernel, then the SwiGLU derivative
             ff = w.shape[1] // 2
-            h = _launch(a, w, offsets, counts, False, covers_all_rows=False).float()
-            gate, up = h[:, :ff], h[:, ff:]
-            sig = torch.sigmoid(gate)
-            g32 = grad_c.float()
-            grad_c = torch.cat([g32 * up * sig * (1 + gate * (1 - sig)), g32 * gate * sig], dim=1).to(a.dtype)
-            del h, gate, up, sig, g32
+            h = _launch(a, w, offsets, counts, False, covers_all_rows=ctx.covers_all_rows)
+            grad_h = torch.empty_like(h)
+            ops._call("fmoe_swiglu_bwd", 1, h.data_ptr(), grad_c.data_ptr(), grad_h.data_ptr(), h.shape[0], ff,
+                      _stream_ptr(h.device))  # fmt: skip
+            grad_c = grad_h
+            del h
         need_a, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        grad_a = _dgrad(grad_c, w, offsets, counts) if need_a else None
+        grad_a = _dgrad(grad_c, w, offsets, counts, ctx.covers_all_rows) if need_a else None
         grad_w = _wgrad(grad_c, a, w.shape, offsets, counts) if need_w else None
         return grad_a, grad_w, None, None, None, None, None
 
 
-def _dgrad(grad_c, w, offsets, counts):
+def _dgrad(grad_c, w, offsets, counts, covers_all_rows=False):
     """grad_a[rows of e] = grad_c[rows of e] @ w[e] on the tensor cores; rows owned by no
     expert get zero."""
     R, N = grad_c.shape
     E, _, K = w.shape
     if N % 64 or K % 256:
         return _dgrad_library(grad_c, w, offsets, counts)
-    grad_a = torch.zeros(R, K, dtype=torch.bfloat16, device=grad_c.device)
+    alloc = torch.empty if covers_all_rows else torch.zeros
+    grad_a = alloc(R, K, dtype=torch.bfloat16, device=grad_c.device)
     ops._call(
         "fmoe_grouped_gemm_dgrad", 1, grad_c.data_ptr(), w.contiguous().data_ptr(), grad_a.data_ptr(),
         offsets.data_ptr(), counts.data_ptr(), E, R, N, K, _status_word(grad_c.device).data_ptr(),

@@ -285,6 +285,15 @@ int fmoe_grouped_gemm_wgrad(const void* grad_c, const void* a, void* grad_w, con
                             const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
                             int32_t* status, void* stream);
 
+/*
+ * Derivative of the fused SwiGLU epilogue: from the pre-activations h = [gate | up]
+ * ([rows, 2*ff] bf16, recomputed with the plain grouped GEMM) and the gradient of
+ * silu(gate) * up ([rows, ff] bf16), writes [d_gate | d_up] ([rows, 2*ff] bf16), the
+ * operand of the gate/up GEMM's data and weight gradients. One streaming pass.
+ */
+int fmoe_swiglu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
+                    void* stream);
+
 /* ---- host-buffer call -------------------------------------------------------- */
 /*
  * The whole combine for a caller that holds HOST memory: copies the E expert
