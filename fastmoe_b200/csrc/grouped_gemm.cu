@@ -701,8 +701,8 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
 }
 
 extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* grad_a, const int64_t* offsets,
-                                       const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
-                                       int32_t* status, void* stream) {
+                                       const int64_t* counts, const int64_t* row_ptrs, int64_t E, int64_t R,
+                                       int64_t N, int64_t K, int32_t* status, void* stream) {
   FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm_dgrad: bad sizes");
   FMOE_REQUIRE(E <= kMaxExperts, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm_dgrad: supports E <= %d", kMaxExperts);
   FMOE_REQUIRE(N % kBK == 0 && K % kBN == 0, FMOE_ERR_UNSUPPORTED,
@@ -711,7 +711,7 @@ extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* 
   FMOE_REQUIRE(R < (1ll << 31) && E * N < (1ll << 31), FMOE_ERR_UNSUPPORTED,
                "fmoe_grouped_gemm_dgrad: R and E*N must fit in int32");
   if (E == 0 || R == 0) return FMOE_OK;
-  FMOE_REQUIRE(grad_c && w && grad_a && offsets && counts, FMOE_ERR_ARG,
+  FMOE_REQUIRE(grad_c && w && (grad_a || row_ptrs) && offsets && counts, FMOE_ERR_ARG,
                "fmoe_grouped_gemm_dgrad: null pointer argument");
   FMOE_REQUIRE(aligned_to(grad_c, 16) && aligned_to(w, 16) && aligned_to(grad_a, 16), FMOE_ERR_ARG,
                "fmoe_grouped_gemm_dgrad: grad_c, w and grad_a must be 16-byte aligned");
@@ -724,7 +724,7 @@ extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* 
   g.offsets = offsets;
   g.counts = counts;
   g.c_row_map = nullptr;
-  g.c_row_ptrs = nullptr;
+  g.c_row_ptrs = row_ptrs;
   g.C = static_cast<__nv_bfloat16*>(grad_a);
   g.ldc = K;
   g.R = R;

@@ -16,8 +16,9 @@ the host, so a call enqueues without ever waiting for the GPU. It replaces
 dispatch_exchange / compute_experts / combine_exchange of polkadot21/fastmoe
 (src/fastmoe/models/tiny_model.py:166-218, :282-294, :308-339) for SwiGLU experts in bf16.
 
-Forward only (inference or activation recomputation); the autograd-capable path is the
-NCCL one. Buffers are symmetric allocations (`torch.distributed._symmetric_memory`) mapped
+`forward` is the gradient-free call; `forward_with_grad` is the training call, whose backward
+sends the gradients the same way (peer-store dispatch of the slot gradients, the gate/up data
+gradient's epilogue storing each row back at its owner). Buffers are symmetric allocations (`torch.distributed._symmetric_memory`) mapped
 into every rank of the group; multicast is not used.
 """
 
@@ -28,6 +29,7 @@ import os
 import torch
 import torch.distributed as dist
 
+from . import exchange
 from .kernels import experts, ops, routing
 from .kernels.ops import _DTYPES, _status_word, _stream_ptr, grouped_weighted_scatter_add
 
@@ -65,7 +67,7 @@ class FusedExpertParallel:
         self.recv_bases = self._peer_addresses(h_recv, self._recv)
         self.ret_bases = self._peer_addresses(h_ret, self._ret)
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self._rows = torch.arange(self.cap_rows, device=self.device)
+        self._grad = None
         dist.barrier(self.group)
 
     def _peer_addresses(self, handle, tensor):
@@ -82,51 +84,80 @@ class FusedExpertParallel:
         """Every rank's earlier work on this stream is complete before anyone's later work starts."""
         dist.all_reduce(self._token, group=self.group)
 
+    # -- the exchange + experts as one differentiable step -------------------------------------
+    def _layout(self, counts):
+        """From everybody's per-expert counts: where my rows go, what my experts receive and
+        where every received row came from. All on the device, fixed-size outputs."""
+        world, E = self.world, self.moe.num_experts
+        C = torch.empty(world, E, dtype=torch.int64, device=counts.device)
+        dist.all_gather_into_tensor(C, counts.contiguous(), group=self.group)
+        return exchange.fused_layout(C, self.rank, self.cap_rows, self.dim * 2)
+
+    def _send_rows(self, rows, expert_of_row, slot_of_row, k, offsets, dst_row0, bases):
+        """Peer-store dispatch of `rows` ([n, D]; row i carries k routed copies) into `bases`."""
+        dev = rows.device
+        ops._call(
+            "fmoe_permute_peer_fwd", 1, rows.data_ptr(), int(rows.stride(0)), expert_of_row.data_ptr(),
+            slot_of_row.data_ptr(), offsets.data_ptr(), dst_row0.data_ptr(), bases.data_ptr(),
+            rows.shape[0], k, self.dim, self.moe.num_experts, self.moe.num_local_experts, self.cap_rows,
+            _DTYPES[rows.dtype], _status_word(dev).data_ptr(), _stream_ptr(dev),
+        )  # fmt: skip
+
+    def _grad_buffers(self):
+        """Second pair of symmetric buffers, for the gradients' trip (allocated on first use)."""
+        if self._grad is None:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            g_recv = symm_mem.empty(self.cap_rows * self.dim, dtype=torch.bfloat16, device=self.device)
+            g_ret = symm_mem.empty(self.max_rows * self.dim, dtype=torch.bfloat16, device=self.device)
+            h1, h2 = symm_mem.rendezvous(g_recv, self.group), symm_mem.rendezvous(g_ret, self.group)
+            self._grad = (g_recv, g_ret, self._peer_addresses(h1, g_recv), self._peer_addresses(h2, g_ret), h1, h2)
+        return self._grad[:4]
+
+    def experts_over_peers(self, x_flat, topk_idx, ix):
+        """Expert outputs for the routed rows of `x_flat`, in this rank's sorted-slot order
+        ([T*K, D], a view of the return buffer), differentiable in x_flat and the expert weights."""
+        return _FusedExperts.apply(x_flat, self.moe.experts.w_gate_up, self.moe.experts.w_down, topk_idx,
+                                   ix.slot_of, ix.offsets, ix.counts, self)  # fmt: skip
+
+    def forward_with_grad(self, x: torch.Tensor) -> torch.Tensor:
+        """The layer with gradients for tokens, router and experts; the forward exchange and
+        the gradients' exchange both ride on peer stores. One forward/backward pair may be in
+        flight per instance (the buffers keep the forward's rows for the backward)."""
+        moe, K = self.moe, self.top_k
+        B, T, D = x.shape
+        n_tok = B * T
+        if n_tok * K > self.max_rows or x.dtype != torch.bfloat16:
+            raise ValueError("the fused path needs bfloat16 input of at most max_tokens tokens")
+        self._grad_buffers()  # collective on first use: here, not inside the backward pass
+        x_flat = x.reshape(n_tok, D)
+        topk_w, topk_idx = routing.route_topk(moe.router(x_flat), K, w_dtype=x.dtype)
+        ix = routing.build_index(topk_idx, topk_w, moe.num_experts, self.world)
+        rows = self.experts_over_peers(x_flat, topk_idx, ix)
+        out = grouped_weighted_scatter_add([rows], ix.reverse_map, ix.sorted_w, (n_tok, D))
+        return out.view(B, T, D)
+
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        moe, world, rank, D, K = self.moe, self.world, self.rank, self.dim, self.top_k
+        moe, world, D, K = self.moe, self.world, self.dim, self.top_k
         B, T, _ = x.shape
         n_tok = B * T
         if n_tok * K > self.max_rows:
             raise ValueError(f"{n_tok} tokens exceed max_tokens={self.max_rows // K} of this FusedExpertParallel")
         if x.dtype != torch.bfloat16:
             raise ValueError("the fused path runs in bfloat16")
-        E, el = moe.num_experts, moe.num_local_experts
+        E = moe.num_experts
         x_flat = x.reshape(n_tok, D)
-        dev = x_flat.device
 
         # routing, as in gate_and_sort
         topk_w, topk_idx = routing.route_topk(moe.router(x_flat), K, w_dtype=x.dtype)
         ix = routing.build_index(topk_idx, topk_w, E, world)
 
-        # everybody's per-expert counts: C[s, e] rows go from rank s to expert e
-        C = torch.empty(world, E, dtype=torch.int64, device=dev)
-        dist.all_gather_into_tensor(C, ix.counts.contiguous(), group=self.group)
-        # receive layout of rank d: expert-major, sources in rank order inside an expert
-        per_dest = C.view(world, world, el).permute(1, 2, 0).reshape(world, el * world)  # [d, (e, s)]
-        seg_start = torch.cumsum(per_dest, 1) - per_dest
-        # where MY rows of expert e begin on its owner (contiguous: the kernel indexes it by expert)
-        dst_row0 = seg_start.view(world, el, world)[:, :, rank].reshape(E).contiguous()
-
-        ops._call(
-            "fmoe_permute_peer_fwd", 1, x_flat.data_ptr(), int(x_flat.stride(0)), topk_idx.data_ptr(),
-            ix.slot_of.data_ptr(), ix.offsets.data_ptr(), dst_row0.data_ptr(), self.recv_bases.data_ptr(),
-            n_tok, K, D, E, el, self.cap_rows, _DTYPES[x.dtype], _status_word(dev).data_ptr(), _stream_ptr(dev),
-        )  # fmt: skip
+        dst_row0, counts_local, offsets_local, src_rank, origin_byte = self._layout(ix.counts)
+        self._send_rows(x_flat, topk_idx, ix.slot_of, K, ix.offsets, dst_row0, self.recv_bases)
         self._barrier()  # all rows for my experts have landed
 
-        # my experts' problem sizes, from the same counts
-        mine = per_dest[rank]  # [(e, s)] sizes of my segments
-        counts_local = mine.view(el, world).sum(1).contiguous()
-        offsets_local = (torch.cumsum(counts_local, 0) - counts_local).contiguous()
-        # return address of every received row: the slot it came from, in its owner's buffer
-        my_start = seg_start[rank]
-        seg = torch.searchsorted(my_start + mine, self._rows, right=True).clamp_(max=el * world - 1)
-        src_rank = seg % world
-        origin_offsets = torch.cumsum(C, 1) - C  # [s, e]: start of expert e in rank s's sorted rows
-        origin_slot = origin_offsets[src_rank, rank * el + seg // world] + (self._rows - my_start[seg])
-        row_ptrs = (self.ret_bases[src_rank] + origin_slot * (D * 2)).contiguous()
-
+        row_ptrs = (self.ret_bases[src_rank] + origin_byte).contiguous()
         recv = self._recv.view(self.cap_rows, D)
         hidden = experts.grouped_gemm(recv, moe.experts.w_gate_up, offsets_local, counts_local, swiglu=True,
                                       covers_all_rows=True)  # fmt: skip
@@ -138,3 +169,67 @@ class FusedExpertParallel:
         return out.view(B, T, D)
 
     __call__ = forward
+
+
+class _FusedExperts(torch.autograd.Function):
+    """rows[slot] = expert(slot)(x[token(slot)]) with both directions of the exchange done by
+    peer stores, forward and backward (see FusedExpertParallel)."""
+
+    @staticmethod
+    def forward(ctx, x_flat, w_gate_up, w_down, topk_idx, slot_of, offsets, counts, fx):
+        D, K = fx.dim, fx.top_k
+        n_rows = x_flat.shape[0] * K
+        dst_row0, counts_local, offsets_local, src_rank, origin_byte = fx._layout(counts)
+        fx._send_rows(x_flat, topk_idx, slot_of, K, offsets, dst_row0, fx.recv_bases)
+        fx._barrier()
+        recv = fx._recv.view(fx.cap_rows, D)
+        hidden = experts._launch(recv, w_gate_up, offsets_local, counts_local, True, covers_all_rows=True)
+        row_ptrs = (fx.ret_bases[src_rank] + origin_byte).contiguous()
+        experts._launch(hidden, w_down, offsets_local, counts_local, False, row_ptrs=row_ptrs)
+        fx._barrier()
+        ctx.fx, ctx.k = fx, K
+        ctx.save_for_backward(w_gate_up, w_down, slot_of, offsets, counts, dst_row0, counts_local,
+                              offsets_local, src_rank, origin_byte, hidden)  # fmt: skip
+        return fx._ret.view(fx.max_rows, D)[:n_rows]
+
+    @staticmethod
+    def backward(ctx, grad_rows):
+        (w_gate_up, w_down, slot_of, offsets, counts, dst_row0, counts_local, offsets_local, src_rank,
+         origin_byte, hidden) = ctx.saved_tensors  # fmt: skip
+        fx, K = ctx.fx, ctx.k
+        D = fx.dim
+        dev = grad_rows.device
+        n_rows = grad_rows.shape[0]
+        g_recv, g_ret, g_recv_bases, g_ret_bases = fx._grad_buffers()
+        grad_rows = grad_rows.contiguous()
+
+        # 1. every slot's gradient row goes to the GPU of its expert, at the row its forward copy took
+        slots = torch.arange(n_rows, device=dev)
+        expert_of_slot = torch.searchsorted(offsets + counts, slots, right=True).clamp_(max=offsets.numel() - 1)
+        fx._send_rows(grad_rows, expert_of_slot.contiguous(), slots.to(torch.int32), 1, offsets, dst_row0, g_recv_bases)
+        fx._barrier()
+
+        # 2. the experts' backward on the rows this rank received (still in the receive buffer)
+        recv = fx._recv.view(fx.cap_rows, D)
+        grad_y = g_recv.view(fx.cap_rows, D)
+        ff = w_down.shape[2]
+        grad_hidden = experts._dgrad(grad_y, w_down, offsets_local, counts_local, covers_all_rows=True)
+        grad_w_down = experts._wgrad(grad_y, hidden, w_down.shape, offsets_local, counts_local)
+        pre = experts._launch(recv, w_gate_up, offsets_local, counts_local, False, covers_all_rows=True)
+        grad_pre = torch.empty_like(pre)
+        ops._call("fmoe_swiglu_bwd", 1, pre.data_ptr(), grad_hidden.data_ptr(), grad_pre.data_ptr(), pre.shape[0], ff,
+                  _stream_ptr(dev))  # fmt: skip
+        grad_w_gate_up = experts._wgrad(grad_pre, recv, w_gate_up.shape, offsets_local, counts_local)
+        # 3. the data gradient's epilogue stores every row back at its owner's slot
+        back_ptrs = (g_ret_bases[src_rank] + origin_byte).contiguous()
+        experts._dgrad(grad_pre, w_gate_up, offsets_local, counts_local, row_ptrs=back_ptrs)
+        fx._barrier()
+
+        # 4. sum the K routed gradients of every token
+        T = n_rows // K
+        grad_x = torch.empty(T, D, dtype=grad_rows.dtype, device=dev)
+        ops._call(
+            "fmoe_permute_bwd", 1, g_ret.data_ptr(), slot_of.data_ptr(), grad_x.data_ptr(), D, T, K, D,
+            _DTYPES[grad_rows.dtype], _stream_ptr(dev),
+        )  # fmt: skip
+        return grad_x, grad_w_gate_up, grad_w_down, None, None, None, None, None

@@ -113,3 +113,34 @@ def regroup_indices(counts_by_source, device, host_counts=None):
     to_rank_major = torch.empty_like(to_expert_major)
     to_rank_major[to_expert_major] = torch.arange(total, device=device)
     return to_expert_major, to_rank_major, tokens_per_expert
+
+
+def fused_layout(C: torch.Tensor, rank: int, cap_rows: int, row_bytes: int):
+    """Placement arithmetic of the fused (peer-store) exchange, from everybody's per-expert
+    counts C[s, e] (rows that rank s routes to global expert e; experts sharded contiguously).
+
+    Every rank lays out what it receives expert-major, sources in rank order inside an expert.
+    Returns, all on C's device and with sizes that do not depend on the data:
+      dst_row0       int64 [E]         row on expert e's owner where THIS rank's rows for e begin
+      counts_local   int64 [E_local]   rows this rank receives per local expert
+      offsets_local  int64 [E_local]   their exclusive prefix sum
+      src_rank       int64 [cap_rows]  source rank of every receive-buffer row
+      origin_byte    int64 [cap_rows]  byte offset, in the source's sorted-slot buffer, of the slot the
+                                       row came from (entries past the received total are meaningless)
+    """
+    world, E = C.shape
+    el = E // world
+    per_dest = C.view(world, world, el).permute(1, 2, 0).reshape(world, el * world)  # [d, (e, s)]
+    seg_start = torch.cumsum(per_dest, 1) - per_dest
+    # contiguous: the kernel indexes it by global expert
+    dst_row0 = seg_start.view(world, el, world)[:, :, rank].reshape(E).contiguous()
+    mine = per_dest[rank]  # sizes of the (e, s) segments this rank receives
+    counts_local = mine.view(el, world).sum(1).contiguous()
+    offsets_local = (torch.cumsum(counts_local, 0) - counts_local).contiguous()
+    rows = torch.arange(cap_rows, device=C.device)
+    my_start = seg_start[rank]
+    seg = torch.searchsorted(my_start + mine, rows, right=True).clamp_(max=el * world - 1)
+    src_rank = seg % world
+    origin_offsets = torch.cumsum(C, 1) - C  # [s, e]: start of expert e in rank s's sorted rows
+    origin_slot = origin_offsets[src_rank, rank * el + seg // world] + (rows - my_start[seg])
+    return dst_row0, counts_local, offsets_local, src_rank, (origin_slot * row_bytes).contiguous()

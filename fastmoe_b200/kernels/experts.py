@@ -84,19 +84,23 @@ class _GroupedGemm(torch.autograd.Function):
         return grad_a, grad_w, None, None, None, None, None
 
 
-def _dgrad(grad_c, w, offsets, counts, covers_all_rows=False):
+def _dgrad(grad_c, w, offsets, counts, covers_all_rows=False, row_ptrs=None):
     """grad_a[rows of e] = grad_c[rows of e] @ w[e] on the tensor cores; rows owned by no
-    expert get zero."""
+    expert get zero. With `row_ptrs` (int64 [R] addresses) every result row is stored where
+    its entry points and nothing is returned."""
     R, N = grad_c.shape
     E, _, K = w.shape
-    if N % 64 or K % 256:
+    if row_ptrs is None and (N % 64 or K % 256):
         return _dgrad_library(grad_c, w, offsets, counts)
-    alloc = torch.empty if covers_all_rows else torch.zeros
-    grad_a = alloc(R, K, dtype=torch.bfloat16, device=grad_c.device)
+    grad_a = None
+    if row_ptrs is None:
+        alloc = torch.empty if covers_all_rows else torch.zeros
+        grad_a = alloc(R, K, dtype=torch.bfloat16, device=grad_c.device)
     ops._call(
-        "fmoe_grouped_gemm_dgrad", 1, grad_c.data_ptr(), w.contiguous().data_ptr(), grad_a.data_ptr(),
-        offsets.data_ptr(), counts.data_ptr(), E, R, N, K, _status_word(grad_c.device).data_ptr(),
-        _stream_ptr(grad_c.device),
+        "fmoe_grouped_gemm_dgrad", 1, grad_c.data_ptr(), w.contiguous().data_ptr(),
+        grad_a.data_ptr() if grad_a is not None else None, offsets.data_ptr(), counts.data_ptr(),
+        row_ptrs.data_ptr() if row_ptrs is not None else None, E, R, N, K,
+        _status_word(grad_c.device).data_ptr(), _stream_ptr(grad_c.device),
     )  # fmt: skip
     return grad_a
 

@@ -267,12 +267,15 @@ int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offs
  * (W[e] is [N, K], read as it lies in memory: its N rows are the reduction dimension and
  * its K columns the output columns, so no transposed copy of the weights is needed). Same
  * kernel, same ragged-row handling and limits as fmoe_grouped_gemm; N must be a multiple of
- * 64 and K of 256. Stands for `g @ w[e]` per expert in the autograd backward of
+ * 64 and K of 256. row_ptrs (optional int64[R] on the device) gives the address of every
+ * output row, as c_row_ptrs does for fmoe_grouped_gemm: the gradients of the dispatched rows
+ * then travel back to the GPUs that own the tokens inside the epilogue (grad_a may be NULL).
+ * Stands for `g @ w[e]` per expert in the autograd backward of
  * MoEFeedForward.compute_experts (src/fastmoe/models/tiny_model.py:282-294).
  */
 int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* grad_a, const int64_t* offsets,
-                            const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
-                            int32_t* status, void* stream);
+                            const int64_t* counts, const int64_t* row_ptrs, int64_t E, int64_t R,
+                            int64_t N, int64_t K, int32_t* status, void* stream);
 
 /*
  * Weight gradient of the grouped GEMM: grad_w[e] = grad_c[rows of e]^T x a[rows of e], bf16

@@ -126,6 +126,24 @@ def _fused_worker(rank, world, port, q):
             with torch.no_grad():
                 results.append((fused(x), moe(x)))
         torch.cuda.synchronize()
+        # training call: forward and backward over peer stores against the NCCL path's autograd
+        xg = torch.randn(1, T, D, generator=torch.Generator(device=dev).manual_seed(900 + rank), device=dev).bfloat16()
+        coeff = torch.randn(1, T, D, generator=torch.Generator(device=dev).manual_seed(901 + rank), device=dev)
+        grads = []
+        for path in (fused.forward_with_grad, moe):
+            for prm in moe.parameters():
+                prm.grad = None
+            xi = xg.clone().requires_grad_(True)
+            yo = path(xi)
+            (yo.float() * coeff).sum().backward()
+            grads.append((yo.detach(), xi.grad, moe.router.weight.grad.clone(), moe.experts.w_gate_up.grad.clone(),
+                          moe.experts.w_down.grad.clone()))  # fmt: skip
+        torch.cuda.synchronize()
+        grad_errs = []
+        for got, want in zip(*grads):
+            scale = float(want.float().abs().max())
+            grad_errs.append(float((got.float() - want.float()).abs().max()) / max(scale, 1e-30))
+
         # the module-level switch routes gradient-free forwards through the same fused path
         moe.enable_fused_exchange(max_tokens=T)
         with torch.no_grad():
@@ -136,6 +154,8 @@ def _fused_worker(rank, world, port, q):
         status = ops.read_status()
         dist.barrier()  # every rank has finished its GPU work before anyone may fail and leave
         assert status == 0
+        # out, d x, d router, d w_gate_up, d w_down: same kernels on both paths, bf16 rounding at most
+        assert max(grad_errs) <= 2e-2, grad_errs
         for got, want in results:
             # same kernels, same row order inside every expert: the two paths must agree exactly
             assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
@@ -152,6 +172,24 @@ def _fused_worker(rank, world, port, q):
     if failure:
         q.put(failure)
         raise SystemExit(1)
+
+
+def test_fused_exchange_single_rank_group():
+    """The same fused path in a process group of ONE rank (its "peer" stores go to its own
+    symmetric buffers): runs on a single-GPU box and covers the forward, the backward and the
+    buffer reuse without a second GPU."""
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    p = ctx.Process(target=_fused_worker, args=(0, 1, _free_port(), q))
+    p.start()
+    p.join(300)
+    msgs = []
+    while not q.empty():
+        msgs.append(q.get())
+    if p.is_alive():
+        p.kill()
+    assert not msgs, "\n".join(msgs)
+    assert p.exitcode == 0
 
 
 def test_fused_exchange_matches_nccl_path_on_two_gpus():

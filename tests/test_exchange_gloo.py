@@ -109,3 +109,46 @@ def test_regroup_indices_small():
     assert np.array_equal(to_rm.numpy(), np.argsort(to_em.numpy()))
     empty = exchange.regroup_indices([[0, 0], [0, 0]], "cpu")
     assert empty[0].numel() == 0 and empty[2] == [0, 0]
+
+
+@pytest.mark.parametrize("world,E,K", [(2, 8, 2), (4, 8, 3), (4, 16, 4)])
+def test_fused_layout_routes_every_row_there_and_back(world, E, K):
+    """The placement arithmetic of the peer-store exchange, emulated with plain tensors: every
+    rank's rows reach the right expert's owner in expert-major order, and the return addresses
+    bring each result back to the slot it came from."""
+    T, D = 40, 3
+    el = E // world
+    cap = world * T * K
+    torch.manual_seed(world * 100 + E)
+    ranks = []
+    for r in range(world):
+        x = torch.randn(T, D)
+        idx, w = routing_uniform(T, E, K, seed=10 + r)
+        rev, _, counts = sort_routing(idx, w, E)
+        order = torch.argsort(idx.reshape(-1), stable=True)
+        slot_of = torch.empty(T * K, dtype=torch.int64)
+        slot_of[order] = torch.arange(T * K)
+        ranks.append(dict(x=x, idx=idx, rev=rev, counts=counts, offsets=torch.cumsum(counts, 0) - counts, slot_of=slot_of))
+    C = torch.stack([r["counts"] for r in ranks])
+    recv = [torch.full((cap, D), float("nan")) for _ in range(world)]
+    ret = [torch.full((T * K, D), float("nan")) for _ in range(world)]
+    layouts = [exchange.fused_layout(C, r, cap, D) for r in range(world)]  # row_bytes = D "bytes" per row
+    for r, rk in enumerate(ranks):  # dispatch: what the permute kernel computes per routed copy
+        dst_row0 = layouts[r][0]
+        for t in range(T):
+            for k in range(K):
+                e = int(rk["idx"][t, k])
+                row = int(dst_row0[e]) + int(rk["slot_of"][t * K + k]) - int(rk["offsets"][e])
+                assert torch.isnan(recv[e // el][row]).all()  # nobody else writes this row
+                recv[e // el][row] = rk["x"][t]
+    for d in range(world):  # experts: scale by (global expert id + 1), then the return stores
+        _, counts_local, offsets_local, src_rank, origin_byte = layouts[d]
+        assert int(counts_local.sum()) == int(C[:, d * el : (d + 1) * el].sum())
+        for e in range(el):
+            for i in range(int(offsets_local[e]), int(offsets_local[e] + counts_local[e])):
+                assert not torch.isnan(recv[d][i]).any()
+                ret[int(src_rank[i])][int(origin_byte[i]) // D] = recv[d][i] * (d * el + e + 1)
+    for r, rk in enumerate(ranks):
+        expert_of_slot = torch.repeat_interleave(torch.arange(E), rk["counts"])
+        want = rk["x"][rk["rev"]] * (expert_of_slot + 1).float()[:, None]
+        assert torch.equal(ret[r], want)
