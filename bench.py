@@ -503,6 +503,33 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, m
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms[0]) / steps
     assert all(bool(torch.isfinite(o.float()).all()) for o in outs)
+
+    # the same layer as a training step: forward + backward (tokens, router and expert gradients)
+    xt = x.view(1, T, D)
+    gy = torch.randn(1, T, D, generator=gen, device=dev, dtype=torch.bfloat16)
+
+    def train_step():
+        for prm in moe.parameters():
+            prm.grad = None
+        xi = xt.detach().requires_grad_(True)
+        y = fused.forward_with_grad(xi) if fused is not None else moe(xi)
+        y.backward(gy)
+        return xi.grad
+
+    train_steps = max(2, min(steps, 5))
+    train_step()
+    barrier()
+    start.record()
+    for _ in range(train_steps):
+        gx = train_step()
+    end.record()
+    barrier()
+    tms = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    train_ms = float(tms[0]) / train_steps
+    assert bool(torch.isfinite(gx.float()).all())
+    del gx, gy
     cpu_baseline = None
     if rank == 0:  # CPU baseline: the expert FFN of a 256-token sample through torch's CPU matmul
         import os
@@ -532,6 +559,8 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, m
         "tokens_per_s": T * world / (ms / 1e3),
         "ms_per_step": ms,
         "tokens_per_rank": T, "micro_batches": MB, "pass": "forward",
+        "train_tokens_per_s": T * world / (train_ms / 1e3), "train_ms_per_step": train_ms,
+        "train_pass": "forward + backward (tokens, router, expert weights), no optimizer",
         "gemm_tflops_per_gpu": gemm_flops / (ms / 1e3) / 1e12,
         "gemm_flops_per_rank": gemm_flops,
         "a2a_bytes_out_per_rank_per_direction": a2a_bytes,
