@@ -54,3 +54,36 @@ def test_workload_routing_is_valid_and_sorted(routing):
     ix = oracle.build_index(idx.numpy(), w.numpy(), E)
     assert np.array_equal(rev.numpy(), ix["reverse_map"]) and np.array_equal(counts.numpy(), ix["counts"])
     assert np.array_equal(sw.numpy(), ix["sorted_w"])
+
+
+def test_expert_and_exchange_wrappers_refuse_cpu_and_bad_shapes():
+    from fastmoe_b200 import ep_fused, exchange
+    from fastmoe_b200.kernels import experts, routing
+
+    a, w = torch.zeros(4, 64, dtype=torch.bfloat16), torch.zeros(1, 256, 64, dtype=torch.bfloat16)
+    cnt = torch.tensor([4])
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        experts.grouped_gemm(a, w, cnt - 4, cnt)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        routing.route_topk(torch.zeros(4, 8), 2)
+    with pytest.raises(RuntimeError, match="process group"):
+        ep_fused.FusedExpertParallel(object(), 16)
+    # the layout arithmetic of the fused exchange is plain tensor code and runs anywhere
+    C = torch.tensor([[3, 0, 2, 1], [1, 4, 0, 2]])
+    dst_row0, counts_local, offsets_local, src_rank, origin_byte = exchange.fused_layout(C, rank=1, cap_rows=16, row_bytes=8)
+    assert counts_local.tolist() == [2, 3] and offsets_local.tolist() == [0, 2]  # rank 1 owns experts 2 and 3
+    # on the owner, experts follow each other and rank 0's rows of an expert precede mine
+    assert dst_row0.tolist() == [3, 4, 2, 3]
+    assert src_rank[:5].tolist() == [0, 0, 0, 1, 1]
+    assert origin_byte[:5].tolist() == [3 * 8, 4 * 8, 5 * 8, 5 * 8, 6 * 8]
+
+
+def test_swiglu_expert_container_behaves_like_a_module_list():
+    from fastmoe_b200.models.tiny_model import GroupedSwiGLUExperts
+
+    ex = GroupedSwiGLUExperts(3, 8, 4)
+    assert len(ex) == 3 and len(list(ex)) == 3 and ex.w_gate_up.shape == (3, 8, 8) and ex.w_down.shape == (3, 8, 4)
+    x = torch.randn(5, 8)
+    h = x @ ex.w_gate_up[1].t()
+    want = (torch.nn.functional.silu(h[:, :4]) * h[:, 4:]) @ ex.w_down[1].t()
+    assert torch.allclose(ex[1](x), want)
