@@ -158,6 +158,52 @@ class MoEFeedForward(nn.Module):
             recv = recv.index_select(0, to_expert_major)
         return recv, splits, send_list, tokens_per_expert
 
+    def _pad_per_rank(self, rows, padded_per_rank, real_per_rank):
+        """[world * real, D] -> [world * padded, D]: every rank's block is followed by zero rows."""
+        block = rows.new_zeros(self.world_size, padded_per_rank, rows.shape[1])
+        block[:, :real_per_rank] = rows.view(self.world_size, real_per_rank, rows.shape[1])
+        return block.view(-1, rows.shape[1])
+
+    def _static_exchange(self, rows, static_splits, real_tokens_per_rank):
+        """Uniform all-to-all of `rows` (the same count to and from every rank, known on the
+        host, so nothing is read back). With splits larger than the real count the blocks are
+        padded with zero rows before the trip and the padding is cut off after it."""
+        splits = list(static_splits)
+        padded = splits[0]
+        if any(s != padded for s in splits) or len(splits) != self.world_size:
+            raise ValueError(f"static_splits must hold one equal count per rank, got {splits}")
+        if rows.shape[0] != real_tokens_per_rank * self.world_size or padded < real_tokens_per_rank:
+            raise ValueError(
+                f"{rows.shape[0]} rows do not make {self.world_size} blocks of {real_tokens_per_rank} "
+                f"(padded to {padded})"
+            )
+        if padded > real_tokens_per_rank:
+            rows = self._pad_per_rank(rows, padded, real_tokens_per_rank)
+        got = exchange.all_to_all_rows(rows, splits, splits, self.group)
+        if padded > real_tokens_per_rank:
+            got = got.view(self.world_size, padded, -1)[:, :real_tokens_per_rank].reshape(-1, got.shape[1])
+        return got
+
+    def dispatch_exchange_static(self, permuted_data, static_splits, real_tokens_per_rank):
+        """Exchange with host-known uniform splits (tiny_model.py:220-280): every rank sends
+        `real_tokens_per_rank` rows to every rank, padded to `static_splits[r]` rows on the
+        wire. Only meaningful when routing really is uniform over ranks; routed rows beyond a
+        rank's block land on the wrong rank, here as in the reference. The exact path is
+        `dispatch_exchange`. Returns (rows, static_splits, static_splits)."""
+        if self.world_size == 1:
+            return permuted_data, static_splits, static_splits
+        recv = self._static_exchange(permuted_data, static_splits, real_tokens_per_rank)
+        return recv, static_splits, static_splits
+
+    def combine_exchange_static(self, expert_output, static_splits, real_tokens_per_rank):
+        """Return trip of `dispatch_exchange_static` (tiny_model.py:341-394). Unlike the
+        reference, which copies the real rows to the front of the padded buffer and so hands
+        most ranks padding, the padding here follows each rank's block: the round trip
+        dispatch -> combine returns every row to where it started, with the same bytes on the wire."""
+        if self.world_size == 1:
+            return expert_output
+        return self._static_exchange(expert_output, static_splits, real_tokens_per_rank)
+
     # -- stage 3 ---------------------------------------------------------------------------
     def expert_outputs(self, recv_data, tokens_per_expert):
         """One output tensor per local expert, left where each expert wrote it."""
@@ -190,6 +236,14 @@ class MoEFeedForward(nn.Module):
             return self._grouped_ffn(recv_data, tokens_per_expert)
         outs = self.expert_outputs(recv_data, tokens_per_expert)
         return torch.cat(outs, dim=0) if outs else recv_data.new_empty(0, self.dim)
+
+    def compute_experts_static(self, recv_data):
+        """Experts over equal shares of the rows (tiny_model.py:296-306): local expert e gets
+        the e-th of `num_local_experts` chunks, sized as torch.chunk sizes them."""
+        n, rows = self.num_local_experts, recv_data.shape[0]
+        size = -(-rows // n) if rows else 0
+        shares = [max(0, min(size, rows - e * size)) for e in range(n)]
+        return self.compute_experts(recv_data, shares)
 
     # -- stage 4 ---------------------------------------------------------------------------
     def combine_exchange(self, expert_output, recv_splits, send_splits):

@@ -152,3 +152,72 @@ def test_fused_layout_routes_every_row_there_and_back(world, E, K):
         expert_of_slot = torch.repeat_interleave(torch.arange(E), rk["counts"])
         want = rk["x"][rk["rev"]] * (expert_of_slot + 1).float()[:, None]
         assert torch.equal(ret[r], want)
+
+
+def _static_worker(rank, world, port, factor, fail_q):
+    """The host-known uniform exchange of the module: every row reaches the rank whose block it
+    sits in, padding never shows, and the return trip undoes the dispatch, gradients included."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from fastmoe_b200 import consts
+        from fastmoe_b200.models.tiny_model import MoEFeedForward
+
+        D, real = 6, 5
+        moe = MoEFeedForward(D, 8, 2 * world, 2, consts.MoEImplementation.STANDARD)
+        rows = (torch.arange(world * real * D, dtype=torch.float64).view(world * real, D) + 1000 * rank)
+        rows.requires_grad_(True)
+        splits = [real * factor] * world
+        recv, s_in, s_out = moe.dispatch_exchange_static(rows, splits, real)
+        assert s_in is splits and s_out is splits and recv.shape == (world * real, D)
+        for src in range(world):  # block `rank` of every source, in source order
+            want = torch.arange(world * real * D, dtype=torch.float64).view(world, real, D)[rank] + 1000 * src
+            assert torch.equal(recv[src * real : (src + 1) * real].detach(), want)
+        shares = moe.compute_experts_static(recv.detach().float())
+        assert shares.shape == (world * real, D)
+        back = moe.combine_exchange_static(recv * 2.0, splits, real)
+        assert torch.equal(back.detach(), rows.detach() * 2.0)
+        coeff = torch.randn(world * real, D, dtype=torch.float64)
+        (back * coeff).sum().backward()
+        assert torch.equal(rows.grad, coeff * 2.0)
+        with pytest.raises(ValueError):
+            moe.dispatch_exchange_static(rows.detach(), [real, real + 1][:world] + [real] * (world - 2), real)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:
+        import traceback
+
+        fail_q.put(f"rank {rank}: {exc}\n{traceback.format_exc()}")
+        raise
+
+
+@pytest.mark.parametrize("factor", [1, 3])
+def test_static_exchange_round_trip(factor):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_static_worker, args=(r, world, port, factor, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    msgs = []
+    while not q.empty():
+        msgs.append(q.get())
+    assert not msgs, "\n".join(msgs)
+    assert all(p.exitcode == 0 for p in procs)
+
+
+def test_static_exchange_single_rank_is_identity():
+    from fastmoe_b200 import consts
+    from fastmoe_b200.models.tiny_model import MoEFeedForward
+
+    moe = MoEFeedForward(4, 8, 3, 2, consts.MoEImplementation.STANDARD)
+    rows = torch.randn(7, 4)
+    got, a, b = moe.dispatch_exchange_static(rows, [14], 7)
+    assert got is rows and a == [14] and b == [14]
+    assert moe.combine_exchange_static(rows, [14], 7) is rows
+    out = moe.compute_experts_static(rows)  # shares of 3, 3, 1 rows
+    want = torch.cat([moe.experts[0](rows[:3]), moe.experts[1](rows[3:6]), moe.experts[2](rows[6:])])
+    assert torch.equal(out, want)
