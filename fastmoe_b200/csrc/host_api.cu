@@ -2,6 +2,7 @@
 // memory. Mirrors grouped_weighted_scatter_add(expert_tensors, indices,
 // weights, out_shape) of polkadot21/fastmoe (src/fastmoe/kernels/ops.py:365-394)
 // for callers outside PyTorch: copies in, plans, gathers, copies out.
+#include <mutex>
 #include <vector>
 
 #include "plan.cuh"
@@ -39,6 +40,55 @@ static ArenaView arena_view(const int64_t* sizes, int64_t E, int64_t N, int64_t 
   a.status = take(sizeof(int32_t));
   a.total = off;
   return a;
+}
+
+extern int g_host_chunks;  // token_major.cu (fmoe_tune "host_chunks")
+
+// Events of one pipelined call, destroyed on every exit path.
+struct EventSet {
+  std::vector<cudaEvent_t> ev;
+  ~EventSet() {
+    for (cudaEvent_t e : ev) cudaEventDestroy(e);
+  }
+  cudaError_t add(cudaEvent_t* out) {
+    const cudaError_t rc = cudaEventCreateWithFlags(out, cudaEventDisableTiming);
+    if (rc == cudaSuccess) ev.push_back(*out);
+    return rc;
+  }
+};
+
+// One non-blocking helper stream per device, created on first use and kept for the
+// life of the process: the gathers and the copies back run there while the caller's
+// stream keeps feeding the copy engine.
+static cudaError_t side_stream(cudaStream_t* out) {
+  constexpr int kMaxDevices = 64;
+  static cudaStream_t streams[kMaxDevices] = {};
+  static std::mutex guard;
+  const std::lock_guard<std::mutex> lock(guard);
+  int dev = 0;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess) return rc;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (streams[dev] == nullptr) {
+    rc = cudaStreamCreateWithFlags(&streams[dev], cudaStreamNonBlocking);
+    if (rc != cudaSuccess) return rc;
+  }
+  *out = streams[dev];
+  return cudaSuccess;
+}
+
+// Columns per slice of the pipelined call: whole 256-byte pieces of a row, slices of
+// at least 4 KB per row (below that the strided copies stop paying).
+static int64_t slice_cols(int64_t D, size_t eb) {
+  const int64_t piece = static_cast<int64_t>(256 / eb);
+  int chunks = g_host_chunks;
+  if (chunks == 0) chunks = static_cast<int64_t>(D * eb) >= 16384 ? 4 : 1;
+  if (chunks <= 1) return D;
+  int64_t cols = (D + chunks - 1) / chunks;
+  cols = (cols + piece - 1) / piece * piece;
+  const int64_t min_cols = static_cast<int64_t>(4096 / eb);
+  if (cols < min_cols) cols = min_cols;
+  return cols < D ? cols : D;
 }
 
 }  // namespace fmoe
@@ -116,6 +166,52 @@ extern "C" int fmoe_combine_host(const void* const* expert_rows_host,
     FMOE_CUDA(cudaMemcpyAsync(base + av.w, w_host, dtype_size(w_dtype) * N, cudaMemcpyHostToDevice, s));
   }
   FMOE_CUDA(cudaMemsetAsync(base + av.status, 0, sizeof(int32_t), s));
+  const int64_t cols = slice_cols(D, eb);
+  if (cols < D) {
+    // Pipelined form (opt-in, fmoe_tune "host_chunks"). The plan needs only the index, the weights and the tables, so it is
+    // built first; the rows then arrive one slice of columns at a time (strided copies on the
+    // caller's stream), and as soon as a slice is complete the helper stream gathers those
+    // columns and sends them back while the next slice is still on its way in: the copy back
+    // travels against the traffic instead of after it.
+    int rc = fmoe_combine_plan(reinterpret_cast<const int64_t*>(base + av.ptr_table),
+                               reinterpret_cast<const int32_t*>(base + av.chunk_sizes),
+                               reinterpret_cast<const int64_t*>(base + av.offsets), base + av.idx,
+                               idx_type, base + av.w, w_dtype, E, N, T, D, dtype, base + av.plan,
+                               av.total - av.plan, reinterpret_cast<int32_t*>(base + av.status), s);
+    if (rc != 0) return rc;
+    cudaStream_t side = nullptr;
+    FMOE_CUDA(side_stream(&side));
+    EventSet events;
+    const size_t pitch = static_cast<size_t>(D) * eb;
+    for (int64_t c0 = 0; c0 < D; c0 += cols) {
+      const int64_t width = (D - c0 < cols ? D - c0 : cols);
+      for (int64_t e = 0; e < E; ++e) {
+        if (chunk_sizes_host[e] > 0)
+          FMOE_CUDA(cudaMemcpy2DAsync(base + row_off[e] + c0 * eb, pitch,
+                                      static_cast<const char*>(expert_rows_host[e]) + c0 * eb, pitch,
+                                      width * eb, static_cast<size_t>(chunk_sizes_host[e]),
+                                      cudaMemcpyHostToDevice, s));
+      }
+      cudaEvent_t arrived;
+      FMOE_CUDA(events.add(&arrived));
+      FMOE_CUDA(cudaEventRecord(arrived, s));
+      FMOE_CUDA(cudaStreamWaitEvent(side, arrived, 0));
+      rc = combine_gather_window(base + av.plan, base + av.out + c0 * eb, D, N, T, c0, width, dtype, side);
+      if (rc != 0) return rc;
+      FMOE_CUDA(cudaMemcpy2DAsync(static_cast<char*>(out_host) + c0 * eb, pitch, base + av.out + c0 * eb,
+                                  pitch, width * eb, static_cast<size_t>(T), cudaMemcpyDeviceToHost, side));
+    }
+    cudaEvent_t returned;
+    FMOE_CUDA(events.add(&returned));
+    FMOE_CUDA(cudaEventRecord(returned, side));
+    FMOE_CUDA(cudaStreamWaitEvent(s, returned, 0));
+    int32_t status_host = 0;
+    FMOE_CUDA(cudaMemcpyAsync(&status_host, base + av.status, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    FMOE_CUDA(cudaStreamSynchronize(s));
+    FMOE_REQUIRE((status_host & FMOE_STATUS_BAD_INDEX) == 0, FMOE_ERR_ARG,
+                 "fmoe_combine_host: an index lies outside [0, T); that row was skipped");
+    return FMOE_OK;
+  }
   for (int64_t e = 0; e < E; ++e) {
     const size_t bytes = static_cast<size_t>(chunk_sizes_host[e]) * D * eb;
     if (bytes > 0)

@@ -47,4 +47,8 @@ inline PlanView plan_view(void* base, int64_t N, int64_t T) {
 // fp32 summation order then varies from run to run).
 constexpr int kPlanStableCap = 1024;
 
+// token_major.cu: the gather over a window of columns (see the definition)
+int combine_gather_window(const void* plan, void* out, int64_t out_row_stride, int64_t N, int64_t T,
+                          int64_t col0, int64_t cols, int dtype, cudaStream_t s);
+
 }  // namespace fmoe

@@ -20,6 +20,7 @@ static int g_gather_v = 0;         // vectors per thread, 0 = choose from D
 static int g_gather_threads = 0;   // threads per CTA, 0 = choose from D
 static int g_gather_ctas_per_sm = -1;  // persistent grid = 148 * this; 0 = one CTA per item; -1 = auto
 static int g_bwd_ctas_per_sm = 3;
+int g_host_chunks = 1;  // column slices of fmoe_combine_host (host_api.cu); 0 = choose from the sizes
 extern int g_gemm_sms, g_gemm_skip_loads, g_gemm_spin_limit;  // grouped_gemm.cu
 
 struct TileCfg {
@@ -73,6 +74,22 @@ struct PlanSource {
   }
   __device__ __forceinline__ void row(int j, const char*& p, float& w) const {
     p = reinterpret_cast<const char*>(src_sorted[j]);
+    w = w_sorted[j];
+  }
+};
+
+struct PlanWindowSource {  // the plan's rows, read from a byte offset inside every row
+  const int32_t* seg_off;
+  const int64_t* src_sorted;
+  const float* w_sorted;
+  int64_t col_bytes;
+  __device__ __forceinline__ void segment(int64_t t, int& beg, int& end) const {
+    beg = seg_off[t];
+    end = seg_off[t + 1];
+  }
+  __device__ __forceinline__ void row(int j, const char*& p, float& w) const {
+    const int64_t a = src_sorted[j];
+    p = a != 0 ? reinterpret_cast<const char*>(a + col_bytes) : nullptr;
     w = w_sorted[j];
   }
 };
@@ -397,6 +414,9 @@ extern "C" int fmoe_tune(const char* key, int value) {
   } else if (k == "bwd_ctas_per_sm") {
     FMOE_REQUIRE(value >= 1 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: bwd_ctas_per_sm in [1, 64]");
     g_bwd_ctas_per_sm = value;
+  } else if (k == "host_chunks") {
+    FMOE_REQUIRE(value >= 0 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: host_chunks in [0, 64]");
+    g_host_chunks = value;
   } else if (k == "gemm_sms") {
     FMOE_REQUIRE(value >= 1 && value <= kNumSMs, FMOE_ERR_ARG, "fmoe_tune: gemm_sms in [1, %d]", kNumSMs);
     g_gemm_sms = value;
@@ -432,6 +452,23 @@ extern "C" int fmoe_combine_gather(const void* plan, void* out, int64_t out_row_
                                                                     accumulate != 0, s)));
   return rc;
 }
+
+namespace fmoe {
+// Columns [col0, col0 + cols) of the combine: sources are read `col0` elements into every planned
+// row, `out` points at column col0 of the output's first row. Used by the host-buffer entry
+// point to finish one slice of columns while the next one is still arriving.
+int combine_gather_window(const void* plan, void* out, int64_t out_row_stride, int64_t N, int64_t T,
+                          int64_t col0, int64_t cols, int dtype, cudaStream_t s) {
+  const PlanView pv = plan_view(const_cast<void*>(plan), N, T);
+  const PlanWindowSource src{pv.seg_off, pv.src_sorted, pv.w_sorted,
+                             col0 * static_cast<int64_t>(dtype_size(dtype))};
+  int rc = 0;
+  FMOE_DISPATCH_DTYPE(dtype, DT,
+                      rc = (launch_gather_sum<DT, true, PlanWindowSource>(src, out, out_row_stride, T,
+                                                                          cols, 0, s)));
+  return rc;
+}
+}  // namespace fmoe
 
 extern "C" int fmoe_combine_bwd(const void* plan, const void* grad_out, int64_t grad_out_row_stride,
                                 void* grad_rows, float* grad_w, int64_t N, int64_t T, int64_t D,
