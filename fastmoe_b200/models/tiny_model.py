@@ -300,15 +300,59 @@ class MoEFeedForward(nn.Module):
         return self.unpermute(final, rev_idx, weights, shape)
 
 
+class FeedForward(nn.Module):
+    """Dense GELU feed-forward of the non-MoE block (tiny_model.py:32-39)."""
+
+    def __init__(self, dim, ff_dim):
+        super().__init__()
+        self.fc1 = nn.Linear(dim, ff_dim, bias=False)
+        self.fc2 = nn.Linear(ff_dim, dim, bias=False)
+
+    def forward(self, x):
+        return self.fc2(F.gelu(self.fc1(x)))
+
+
+class _ResidualBlock(nn.Module):
+    """Pre-norm attention and feed-forward with residual connections; `self.ff` is set by the subclass."""
+
+    def __init__(self, dim, n_heads):
+        super().__init__()
+        self.norm1 = nn.LayerNorm(dim)
+        self.attn = MultiheadSelfAttention(dim, n_heads)
+        self.norm2 = nn.LayerNorm(dim)
+
+    def forward(self, x):
+        x = x + self.attn(self.norm1(x))
+        return x + self.ff(self.norm2(x))
+
+
+class Block(_ResidualBlock):
+    """Dense transformer block (tiny_model.py:424-435)."""
+
+    def __init__(self, dim, n_heads, ff_dim):
+        super().__init__(dim, n_heads)
+        self.ff = FeedForward(dim, ff_dim)
+
+
+class MoEBlock(_ResidualBlock):
+    """Transformer block whose feed-forward is a `MoEFeedForward` (tiny_model.py:438-463)."""
+
+    def __init__(self, dim, n_heads, ff_dim, num_experts, top_k, implementation, expert_type="gelu"):
+        super().__init__(dim, n_heads)
+        self.ff = MoEFeedForward(dim, ff_dim, num_experts, top_k, implementation, expert_type=expert_type)
+
+
 class PipelinedMoEBlock(nn.Module):
     """Attention + MoE block that splits the batch into micro-batches and overlaps one
     micro-batch's token exchange with another's compute on separate CUDA streams
     (tiny_model.py:466-630 uses two micro-batches on `stream0`/`stream1`; here
     `num_micro_batches` may be larger and further streams are created on demand).
-    Exchanges are the exact, dynamically sized ones."""
+    Exchanges are the exact, dynamically sized ones. Left at None, the number of micro-batches
+    is 2 with several ranks and 1 with a single rank: without an exchange there is nothing to
+    overlap, and splitting the batch only doubles the per-expert launches."""
 
     def __init__(self, dim, n_heads, ff_dim, num_experts, top_k, stream0, stream1,
-                 comm_balance_factor=1, num_micro_batches=2, expert_type="gelu"):  # fmt: skip
+                 comm_balance_factor=1, num_micro_batches=None, expert_type="gelu"):  # fmt: skip
         super().__init__()
         self.norm1 = nn.LayerNorm(dim)
         self.attn = MultiheadSelfAttention(dim, n_heads)
@@ -321,13 +365,23 @@ class PipelinedMoEBlock(nn.Module):
         self._extra_streams = []
 
     def _streams(self, n):
+        if self.stream0 is None:  # a caller without streams of its own gets two from the block
+            self.stream0 = torch.cuda.Stream()
+        if self.stream1 is None:
+            self.stream1 = torch.cuda.Stream()
         streams = [self.stream0, self.stream1]
         while len(streams) + len(self._extra_streams) < n:
             self._extra_streams.append(torch.cuda.Stream())
         return (streams + self._extra_streams)[:n]
 
     def forward(self, x):
-        chunks = x.chunk(self.num_micro_batches, dim=0)
+        n_mb = self.num_micro_batches
+        if n_mb is None:
+            n_mb = 2 if self.moe.world_size > 1 else 1
+        if n_mb == 1:  # nothing to overlap: the plain block on the caller's stream
+            x = x + self.attn(self.norm1(x))
+            return x + self.moe(self.norm2(x))
+        chunks = x.chunk(n_mb, dim=0)
         streams = self._streams(len(chunks))
         main = torch.cuda.current_stream()
         resid, moe_in = [], []
@@ -400,3 +454,43 @@ def pipelined_moe_forward(moe, inputs, streams):
                 outs[i] = moe.unpermute(fd, rev, w, shape)
         gated[i] = dispatched[i] = None
     return outs
+
+
+class TinyModel(nn.Module):
+    """Input projection, `n_layers` blocks, output projection (tiny_model.py:634-699).
+
+    The block type follows the reference: dense `Block` without MoE, `MoEBlock` for the
+    STANDARD implementation, `PipelinedMoEBlock` for FAST. `top_k`, `stream0` and `stream1`
+    may be left out (the reference's own training benchmark calls the constructor without
+    them, run_on_cloud.py:111-121, which its signature rejects): top_k then defaults to 2
+    and the pipelined blocks create their streams on first use.
+    """
+
+    def __init__(self, in_dim, dim, n_heads, ff_dim, n_layers, num_experts=None, top_k=None,
+                 implementation=None, stream0=None, stream1=None, comm_balance_factor=1, *,
+                 use_moe, expert_type="gelu", num_micro_batches=None):  # fmt: skip
+        super().__init__()
+        self.inp = nn.Linear(in_dim, dim, bias=False)
+        if use_moe:
+            if num_experts is None:
+                raise ValueError("use_moe=True needs num_experts")
+            top_k = 2 if top_k is None else top_k
+        if not use_moe:
+            blocks = [Block(dim, n_heads, ff_dim) for _ in range(n_layers)]
+        elif implementation == consts.MoEImplementation.STANDARD:
+            blocks = [MoEBlock(dim, n_heads, ff_dim, num_experts, top_k, implementation, expert_type)
+                      for _ in range(n_layers)]  # fmt: skip
+        elif implementation == consts.MoEImplementation.FAST:
+            blocks = [PipelinedMoEBlock(dim, n_heads, ff_dim, num_experts, top_k, stream0, stream1,
+                                        comm_balance_factor, num_micro_batches, expert_type)
+                      for _ in range(n_layers)]  # fmt: skip
+        else:
+            raise NotImplementedError(f"implementation {implementation!r}")
+        self.blocks = nn.ModuleList(blocks)
+        self.out = nn.Linear(dim, in_dim, bias=False)
+
+    def forward(self, x):
+        x = self.inp(x)
+        for block in self.blocks:
+            x = block(x)
+        return self.out(x)
