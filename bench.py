@@ -69,6 +69,7 @@ GEMM = {
     "grouped_swiglu_ffn_E32_R65536_D7168_ff2048": (32, 65536, 7168, 2048),  # one rank of 8
     "grouped_swiglu_ffn_E256_R65536_D7168_ff2048": (256, 65536, 7168, 2048),  # a single rank
     "grouped_swiglu_ffn_ncu_E8_R8192_D7168_ff2048": (8, 8192, 7168, 2048),  # small case for ncu
+    "grouped_swiglu_ffn_ncu_E32_R8192_D7168_ff2048": (32, 8192, 7168, 2048),  # 256 rows per expert, for ncu
 }
 
 # DRAM bytes (read + write) of one gather launch on the default workload: the ncu
@@ -804,6 +805,8 @@ def main():
                     help="expert-parallel layer with several ranks: fused peer-store exchange or NCCL all-to-all")
     ap.add_argument("--gemm-sms", type=int, default=None, help="expert-parallel layer: SMs for the grouped GEMM")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel layer part of the default run")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="launch-shape knob of the library (fmoe_tune), for sweeps; repeatable")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -820,6 +823,11 @@ def main():
 
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    for item in args.tune:
+        from fastmoe_b200 import _lib
+
+        key, _, val = item.partition("=")
+        _lib.tune(key, int(val))
     try:
         if args.workload in CFG4:
             run_cfg4(args, rank, world, local_rank)

@@ -48,6 +48,7 @@ struct GemmArgs {
   int swiglu;
   int w_transposed;        // 1: data gradient, C = A x W (W is [E, K_red, N_out]: the reduction runs over W's rows)
   int skip_loads;  // test hook: the producer issues nothing, so every consumer wait runs out
+  int prefetch;    // weight k-blocks requested into L2 ahead of the loads (0 = none)
   uint32_t spin_limit;
   int32_t* status;
 };
@@ -147,6 +148,11 @@ constexpr uint32_t kIdescBMn = kIdesc | (1u << 16);  // B with the N dimension c
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
+// Asks for a tile to be brought into L2; completes on its own, nothing waits for it.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1)
+               : "memory");
+}
 struct TileCoord {
   int expert, mb, nb, rows;  // rows = valid rows of this M block
   int64_t row0;              // first row in A / C
@@ -240,11 +246,43 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // ---- TMA producer ---------------------------------------------------------------
     int stage = 0;
     uint32_t phase = 0;
+    // Optional (fmoe_tune "gemm_prefetch", off by default): ask for the weight k-blocks
+    // `a.prefetch` steps ahead (across the boundary to this CTA's next tile) to be brought
+    // into L2, so that the loads themselves find them there.
+    auto prefetch_w = [&](int expert, int nb, int kb) {
+      if (a.w_transposed) {
+        const int red_row = expert * a.w_rows_per_expert + kb * kBK;
+#pragma unroll
+        for (int piece = 0; piece < 4; ++piece) tma_prefetch_2d(&map_w, nb * kBN + piece * 64, red_row);
+      } else {
+        const int r0 = expert * a.w_rows_per_expert + nb * (a.swiglu ? 128 : kBN);
+        tma_prefetch_2d(&map_w, kb * kBK, r0);
+        tma_prefetch_2d(&map_w, kb * kBK, r0 + a.up_row_offset);
+      }
+    };
+    const int ahead = a.prefetch < a.k_blocks ? a.prefetch : a.k_blocks;
+    bool first_tile = true;
     for (int tile = blockIdx.x; tile < total_tiles && !a.skip_loads; tile += gridDim.x) {
       const TileCoord c = locate_tile(tile, mb_prefix, a);
       const int w_row0 = c.expert * a.w_rows_per_expert + c.nb * (a.swiglu ? 128 : kBN);
       const int w_row1 = w_row0 + a.up_row_offset;
+      int next_expert = -1, next_nb = 0;
+      if (ahead > 0) {
+        if (first_tile)
+          for (int kb = 0; kb < ahead; ++kb) prefetch_w(c.expert, c.nb, kb);
+        first_tile = false;
+        if (tile + static_cast<int>(gridDim.x) < total_tiles) {
+          const TileCoord n = locate_tile(tile + gridDim.x, mb_prefix, a);
+          next_expert = n.expert;
+          next_nb = n.nb;
+        }
+      }
       for (int kb = 0; kb < a.k_blocks; ++kb) {
+        if (ahead > 0) {
+          const int pk = kb + ahead;
+          if (pk < a.k_blocks) prefetch_w(c.expert, c.nb, pk);
+          else if (next_expert >= 0) prefetch_w(next_expert, next_nb, pk - a.k_blocks);
+        }
         if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
         mbar_expect_tx(&full[stage], kStageBytes);
         tma_load_2d(smem_a + stage * kABytes, &map_a, kb * kBK, static_cast<int>(c.row0), &full[stage]);
@@ -599,6 +637,13 @@ int g_gemm_sms = kNumSMs;
 // Test hooks (fmoe_tune "gemm_skip_loads", "gemm_spin_limit"): make the bounded waits run out
 // on purpose, with a short limit, to exercise the give-up path without hanging anything.
 int g_gemm_skip_loads = 0;
+// fmoe_tune "gemm_prefetch": weight k-blocks to request into L2 ahead of the loads. Off unless
+// asked for: measured on B200 it costs more than it returns in both regimes (256 rows per expert:
+// 6.13 ms without, 6.93 / 6.74 / 8.03 ms with 8 / 16 / 32 k-blocks ahead; 2048 rows per expert:
+// 4.62 ms without, 5.07-5.15 ms with), because the requests go through the same TMA unit and
+// fill path as the loads, which are already close to their per-SM limit.
+int g_gemm_prefetch = 0;
+static int prefetch_depth(int64_t, int64_t) { return g_gemm_prefetch > 0 ? g_gemm_prefetch : 0; }
 int g_gemm_spin_limit = static_cast<int>(kSpinLimit);
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -685,6 +730,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   g.swiglu = swiglu ? 1 : 0;
   g.w_transposed = 0;
   g.skip_loads = g_gemm_skip_loads;
+  g.prefetch = prefetch_depth(R, E);
   g.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
   g.status = status;
 
@@ -736,6 +782,7 @@ extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* 
   g.swiglu = 0;
   g.w_transposed = 1;
   g.skip_loads = g_gemm_skip_loads;
+  g.prefetch = prefetch_depth(R, E);
   g.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
   g.status = status;
   const size_t smem = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + kEpiStageBytes + sizeof(int) * (E + 2);
