@@ -57,6 +57,7 @@ class FusedExpertParallel:
         self.device = moe.router.weight.device
         self.dim, self.top_k = moe.dim, moe.top_k
         self.max_rows = int(max_tokens) * moe.top_k
+        self._generation = 0  # forwards run so far: a backward checks that it belongs to the latest
         self.cap_rows = int(min(capacity_factor, self.world) * self.max_rows)
         self.cap_rows = (self.cap_rows + 127) // 128 * 128
         self._recv = symm_mem.empty(self.cap_rows * self.dim, dtype=torch.bfloat16, device=self.device)
@@ -130,6 +131,7 @@ class FusedExpertParallel:
         if n_tok * K > self.max_rows or x.dtype != torch.bfloat16:
             raise ValueError("the fused path needs bfloat16 input of at most max_tokens tokens")
         self._grad_buffers()  # collective on first use: here, not inside the backward pass
+        self._generation += 1  # a backward of an earlier forward now refuses to run
         x_flat = x.reshape(n_tok, D)
         topk_w, topk_idx = routing.route_topk(moe.router(x_flat), K, w_dtype=x.dtype)
         ix = routing.build_index(topk_idx, topk_w, moe.num_experts, self.world)
@@ -148,6 +150,7 @@ class FusedExpertParallel:
             raise ValueError("the fused path runs in bfloat16")
         E = moe.num_experts
         x_flat = x.reshape(n_tok, D)
+        self._generation += 1  # overwrites the buffers a pending backward would read
 
         # routing, as in gate_and_sort
         topk_w, topk_idx = routing.route_topk(moe.router(x_flat), K, w_dtype=x.dtype)
@@ -188,6 +191,7 @@ class _FusedExperts(torch.autograd.Function):
         experts._launch(hidden, w_down, offsets_local, counts_local, False, row_ptrs=row_ptrs)
         fx._barrier()
         ctx.fx, ctx.k = fx, K
+        ctx.generation = fx._generation
         ctx.save_for_backward(w_gate_up, w_down, slot_of, offsets, counts, dst_row0, counts_local,
                               offsets_local, src_rank, origin_byte, hidden)  # fmt: skip
         return fx._ret.view(fx.max_rows, D)[:n_rows]
@@ -197,6 +201,12 @@ class _FusedExperts(torch.autograd.Function):
         (w_gate_up, w_down, slot_of, offsets, counts, dst_row0, counts_local, offsets_local, src_rank,
          origin_byte, hidden) = ctx.saved_tensors  # fmt: skip
         fx, K = ctx.fx, ctx.k
+        if ctx.generation != fx._generation:
+            raise RuntimeError(
+                "FusedExpertParallel: another forward ran on this layer before the backward of an earlier "
+                "one; the exchange buffers keep one forward's rows, so those gradients would be wrong. "
+                "Run each forward's backward before the next forward (or use the NCCL path)."
+            )
         D = fx.dim
         dev = grad_rows.device
         n_rows = grad_rows.shape[0]

@@ -144,6 +144,17 @@ def _fused_worker(rank, world, port, q):
             scale = float(want.float().abs().max())
             grad_errs.append(float((got.float() - want.float()).abs().max()) / max(scale, 1e-30))
 
+        # the buffers keep ONE forward's rows: the backward of an overtaken forward must refuse
+        y_old = fused.forward_with_grad(xg.clone().requires_grad_(True))
+        y_new = fused.forward_with_grad(xg.clone().requires_grad_(True))
+        try:
+            y_old.float().sum().backward()
+            stale_refused = False
+        except RuntimeError as exc:
+            stale_refused = "another forward" in str(exc)
+        y_new.float().sum().backward()  # the latest forward's backward still runs
+        torch.cuda.synchronize()
+
         # the module-level switch routes gradient-free forwards through the same fused path
         moe.enable_fused_exchange(max_tokens=T)
         with torch.no_grad():
@@ -154,6 +165,7 @@ def _fused_worker(rank, world, port, q):
         status = ops.read_status()
         dist.barrier()  # every rank has finished its GPU work before anyone may fail and leave
         assert status == 0
+        assert stale_refused, "a backward ran on exchange buffers that a later forward had overwritten"
         # out, d x, d router, d w_gate_up, d w_down: same kernels on both paths, bf16 rounding at most
         assert max(grad_errs) <= 2e-2, grad_errs
         for got, want in results:
