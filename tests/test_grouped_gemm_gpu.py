@@ -43,6 +43,8 @@ CASES = [
     ([1] * 40, 128, 256, False),  # many one-row experts
     ([700, 33], 7168, 256, False),  # deep K: the pipeline wraps many times
     ([513, 127, 129], 1024, 1024, True),
+    ([256, 257, 16, 17, 270, 0, 255], 256, 512, True),  # around the row-block boundaries
+    ([256, 257, 16, 17, 270, 0, 255], 256, 512, False),
 ]
 
 
