@@ -26,3 +26,14 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     assert d["steps"] == 2 and d["value"] > 0 and d["config"]["workload"].startswith("combine_small")
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"]
+
+
+def test_reference_arm_on_another_rank_exits_quietly():
+    """Under a multi-rank launch only rank 0 times the CPU path; the others print nothing and exit 0."""
+    env = {"CUDA_VISIBLE_DEVICES": "", "PATH": "/usr/bin:/bin", "RANK": "1", "LOCAL_RANK": "1", "WORLD_SIZE": "2"}
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"],
+        capture_output=True, text=True, timeout=120, env=env,
+    )  # fmt: skip
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert not [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
