@@ -46,6 +46,7 @@ SIGNATURES = {
     "fmoe_grouped_gemm_dgrad": (c_int, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "fmoe_grouped_gemm_wgrad": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "fmoe_swiglu_bwd": (c_int, [_P, _P, _P, _L, _L, _P]),
+    "fmoe_swiglu_bwd_ragged": (c_int, [_P, _P, _P, _L, _L, _P, _P]),
     "fmoe_permute_peer_fwd": (c_int, [_P, _L, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P, _P]),
     "fmoe_combine_host_arena_bytes": (c_size_t, [_P, _L, _L, _L, _L, _I]),
     "fmoe_combine_host": (c_int, [_P, _P, _P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, c_size_t, _P]),

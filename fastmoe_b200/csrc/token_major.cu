@@ -591,7 +591,11 @@ extern "C" int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_o
 namespace fmoe {
 __global__ void __launch_bounds__(256)
     swiglu_bwd_kernel(const uint4* __restrict__ h, const uint4* __restrict__ g, uint4* __restrict__ dh,
-                      int64_t rows, int64_t ffvec) {
+                      int64_t rows, int64_t ffvec, const int64_t* __restrict__ rows_used) {
+  if (rows_used != nullptr) {  // a capacity-sized buffer: only its first *rows_used rows hold data
+    const int64_t used = *rows_used;
+    rows = used < 0 ? 0 : (used < rows ? used : rows);
+  }
   const int64_t total = rows * ffvec;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -614,6 +618,11 @@ __global__ void __launch_bounds__(256)
 
 extern "C" int fmoe_swiglu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
                                void* stream) {
+  return fmoe_swiglu_bwd_ragged(h, grad_act, grad_h, rows, ff, nullptr, stream);
+}
+
+extern "C" int fmoe_swiglu_bwd_ragged(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
+                                      const int64_t* rows_used, void* stream) {
   FMOE_REQUIRE(rows >= 0 && ff >= 0, FMOE_ERR_ARG, "fmoe_swiglu_bwd: negative size");
   FMOE_REQUIRE(ff % 8 == 0, FMOE_ERR_UNSUPPORTED, "fmoe_swiglu_bwd: ff=%lld must be a multiple of 8", (long long)ff);
   if (rows == 0 || ff == 0) return FMOE_OK;
@@ -624,6 +633,7 @@ extern "C" int fmoe_swiglu_bwd(const void* h, const void* grad_act, void* grad_h
   const int64_t blocks = (total + 255) / 256;
   const int grid = static_cast<int>(blocks < kNumSMs * 8 ? blocks : kNumSMs * 8);
   swiglu_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(h), static_cast<const uint4*>(grad_act), static_cast<uint4*>(grad_h), rows, ff / 8);
+      static_cast<const uint4*>(h), static_cast<const uint4*>(grad_act), static_cast<uint4*>(grad_h), rows, ff / 8,
+      rows_used);
   return check_launch("swiglu_bwd_kernel");
 }

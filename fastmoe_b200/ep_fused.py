@@ -227,8 +227,9 @@ class _FusedExperts(torch.autograd.Function):
         grad_w_down = experts._wgrad(grad_y, hidden, w_down.shape, offsets_local, counts_local)
         pre = experts._launch(recv, w_gate_up, offsets_local, counts_local, False, covers_all_rows=True)
         grad_pre = torch.empty_like(pre)
-        ops._call("fmoe_swiglu_bwd", 1, pre.data_ptr(), grad_hidden.data_ptr(), grad_pre.data_ptr(), pre.shape[0], ff,
-                  _stream_ptr(dev))  # fmt: skip
+        rows_used = counts_local.sum(dtype=torch.int64).reshape(1)  # the buffers are sized for the worst case
+        ops._call("fmoe_swiglu_bwd_ragged", 1, pre.data_ptr(), grad_hidden.data_ptr(), grad_pre.data_ptr(),
+                  pre.shape[0], ff, rows_used.data_ptr(), _stream_ptr(dev))  # fmt: skip
         grad_w_gate_up = experts._wgrad(grad_pre, recv, w_gate_up.shape, offsets_local, counts_local)
         # 3. the data gradient's epilogue stores every row back at its owner's slot
         back_ptrs = (g_ret_bases[src_rank] + origin_byte).contiguous()

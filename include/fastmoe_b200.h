@@ -301,6 +301,11 @@ int fmoe_grouped_gemm_wgrad(const void* grad_c, const void* a, void* grad_w, con
  */
 int fmoe_swiglu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
                     void* stream);
+/* The same over a capacity-sized buffer whose row count lives on the device: only the first
+ * min(rows, *rows_used) rows are read and written (rows_used may be NULL = all rows). Used
+ * by the fused expert-parallel exchange, whose receive buffers are sized for the worst case. */
+int fmoe_swiglu_bwd_ragged(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
+                           const int64_t* rows_used, void* stream);
 
 /* ---- host-buffer call -------------------------------------------------------- */
 /*

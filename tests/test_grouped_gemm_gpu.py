@@ -164,3 +164,32 @@ def test_backward_on_tensor_cores_matches_fp32_autograd(counts, K, N, swiglu):
         err = float((got.float() - want).abs().max() / want.abs().max())
         assert err <= REL_TOL[torch.bfloat16], (what, err)
     assert float(w.grad[1].abs().max()) == 0.0 if counts[1:2] == [0] else True  # an expert without rows
+
+
+def test_swiglu_derivative_over_a_capacity_sized_buffer():
+    """fmoe_swiglu_bwd_ragged touches only the rows a device-side count names; the plain entry
+    point is the same kernel over all rows. Checked against autograd of silu(gate) * up in fp32."""
+    from fastmoe_b200.kernels.ops import _stream_ptr
+
+    rows, used, ff = 96, 41, 256
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    h = torch.randn(rows, 2 * ff, generator=gen, device=DEV).bfloat16()
+    g = torch.randn(rows, ff, generator=gen, device=DEV).bfloat16()
+    hf = h.float().requires_grad_(True)
+    (torch.nn.functional.silu(hf[:, :ff]) * hf[:, ff:] * g.float()).sum().backward()
+    want = hf.grad
+    sentinel = 7.0
+    for count in (used, None):
+        out = torch.full_like(h, sentinel)
+        if count is None:
+            ops._call("fmoe_swiglu_bwd", 1, h.data_ptr(), g.data_ptr(), out.data_ptr(), rows, ff, _stream_ptr(h.device))
+            n = rows
+        else:
+            cnt = torch.tensor([count], dtype=torch.int64, device=DEV)
+            ops._call("fmoe_swiglu_bwd_ragged", 1, h.data_ptr(), g.data_ptr(), out.data_ptr(), rows, ff,
+                      cnt.data_ptr(), _stream_ptr(h.device))  # fmt: skip
+            n = count
+        torch.cuda.synchronize()
+        err = float((out[:n].float() - want[:n]).abs().max() / want.abs().max())
+        assert err <= REL_TOL[torch.bfloat16], err
+        assert bool((out[n:] == sentinel).all()), "rows past the count were written"
