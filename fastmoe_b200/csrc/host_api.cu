@@ -57,6 +57,18 @@ struct EventSet {
   }
 };
 
+// Waits for both streams of a pipelined call when it is left early (an error part-way through):
+// nothing of the call may still be running when the caller sees the status.
+struct DrainOnExit {
+  cudaStream_t a, b;
+  bool armed = true;
+  ~DrainOnExit() {
+    if (!armed) return;
+    cudaStreamSynchronize(b);
+    cudaStreamSynchronize(a);
+  }
+};
+
 // One non-blocking helper stream per device, created on first use and kept for the
 // life of the process: the gathers and the copies back run there while the caller's
 // stream keeps feeding the copy engine.
@@ -182,6 +194,7 @@ extern "C" int fmoe_combine_host(const void* const* expert_rows_host,
     cudaStream_t side = nullptr;
     FMOE_CUDA(side_stream(&side));
     EventSet events;
+    DrainOnExit drain{s, side};
     const size_t pitch = static_cast<size_t>(D) * eb;
     for (int64_t c0 = 0; c0 < D; c0 += cols) {
       const int64_t width = (D - c0 < cols ? D - c0 : cols);
@@ -208,6 +221,7 @@ extern "C" int fmoe_combine_host(const void* const* expert_rows_host,
     int32_t status_host = 0;
     FMOE_CUDA(cudaMemcpyAsync(&status_host, base + av.status, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
     FMOE_CUDA(cudaStreamSynchronize(s));
+    drain.armed = false;  // s has waited for the helper stream: both are idle
     FMOE_REQUIRE((status_host & FMOE_STATUS_BAD_INDEX) == 0, FMOE_ERR_ARG,
                  "fmoe_combine_host: an index lies outside [0, T); that row was skipped");
     return FMOE_OK;
