@@ -21,6 +21,8 @@ STATUS_BAD_EXPERT = 2
 STATUS_NULL_PTR = 4
 STATUS_WAIT_TIMEOUT = 8
 
+ACT_NONE, ACT_SWIGLU, ACT_GELU = 0, 1, 2
+
 _P = c_void_p
 _I = c_int
 _L = c_int64
@@ -46,8 +48,11 @@ SIGNATURES = {
     "fmoe_grouped_gemm_dgrad": (c_int, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "fmoe_grouped_gemm_wgrad": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "fmoe_swiglu_bwd": (c_int, [_P, _P, _P, _L, _L, _P]),
+    "fmoe_gelu_bwd": (c_int, [_P, _P, _P, _L, _L, _P]),
     "fmoe_swiglu_bwd_ragged": (c_int, [_P, _P, _P, _L, _L, _P, _P]),
-    "fmoe_permute_peer_fwd": (c_int, [_P, _L, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P, _P]),
+    "fmoe_permute_peer_fwd": (c_int, [_P, _L, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P, _L, _L, _I, _P, _P]),
+    "fmoe_peer_barrier": (c_int, [_P, _L, _L, ctypes.c_int32, _L, _P, _P]),
+    "fmoe_ep_layout": (c_int, [_P, _L, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "fmoe_combine_host_arena_bytes": (c_size_t, [_P, _L, _L, _L, _L, _I]),
     "fmoe_combine_host": (c_int, [_P, _P, _P, _I, _P, _I, _P, _L, _L, _L, _L, _I, _P, c_size_t, _P]),
 }

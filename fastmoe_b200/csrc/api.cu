@@ -31,7 +31,7 @@ int check_cuda(cudaError_t e, const char* what) {
 
 extern "C" {
 
-int fmoe_abi_version(void) { return 1; }
+int fmoe_abi_version(void) { return 2; }
 
 const char* fmoe_last_error(void) { return fmoe::g_last_error; }
 

@@ -200,15 +200,6 @@ __device__ __forceinline__ uint4 ld_stream16(const uint4* p) {
                : "l"(p));
   return v;
 }
-// Rows that are read again soon by another CTA (the K reads of one grad_out
-// row): normal L2 policy.
-__device__ __forceinline__ uint4 ld_keep16(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
 // Rows that several warps of one CTA read at about the same time: let L1 keep them.
 __device__ __forceinline__ uint4 ld_cached16(const uint4* p) {
   uint4 v;

@@ -46,6 +46,7 @@ struct GemmArgs {
   int w_rows_per_expert;   // rows of the weight tensor per expert (N, or 2*ff for SwiGLU)
   int up_row_offset;       // SwiGLU: row of the first "up" weight inside an expert (= ff), else 128
   int swiglu;
+  int gelu;                // plain product followed by the exact (erf) GELU, as nn.GELU() computes it
   int w_transposed;        // 1: data gradient, C = A x W (W is [E, K_red, N_out]: the reduction runs over W's rows)
   int skip_loads;  // test hook: the producer issues nothing, so every consumer wait runs out
   int prefetch;    // weight k-blocks requested into L2 ahead of the loads (0 = none)
@@ -84,6 +85,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if ((spin & 1023u) == 1023u && *abort_flag) return false;
   }
   return false;
+}
+// The same without the give-up flag: used on the way out, when the flag may already be set.
+__device__ __forceinline__ bool mbar_wait_plain(uint64_t* bar, uint32_t parity, uint32_t limit) {
+  int never = 0;
+  return mbar_wait(bar, parity, &never, limit);
+}
+// Leaving the kernel, normally or after a wait gave up: the MMA thread waits (bounded) until
+// the tensor core has finished every MMA it issued, so that tensor memory is not released
+// under them; after a give-up the producer thread waits (bounded) for the loads it still has
+// in flight, so that none lands in shared memory after the CTA has gone.
+__device__ __forceinline__ void drain_on_exit(int warp, int lane, int fills, bool mma_issued, uint64_t* full,
+                                              uint64_t* drain, const volatile int* abort_flag, int stages,
+                                              uint32_t limit) {
+  if (warp == 0 && lane == 0 && *abort_flag) {
+    for (int s = 0; s < stages && s < fills; ++s) {
+      const int last = (fills - 1 - s) / stages * stages + s;  // last fill that used stage s
+      mbar_wait_plain(&full[s], (last / stages) & 1, limit);
+    }
+  }
+  if (warp == 1 && lane == 0 && mma_issued) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     static_cast<uint32_t>(__cvta_generic_to_shared(drain)))
+                 : "memory");
+    mbar_wait_plain(drain, 0, limit);
+  }
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile(
@@ -147,6 +173,15 @@ constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 
 constexpr uint32_t kIdescBMn = kIdesc | (1u << 16);  // B with the N dimension contiguous
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+// Rows of expert e that lie inside A: a count that would run past the end of A (a caller
+// whose receive buffer overflowed, say) is cut there, so no tile reaches beyond row R.
+__device__ __forceinline__ int64_t expert_rows(const int64_t* offsets, const int64_t* counts, int64_t R, int e) {
+  const int64_t off = offsets[e], n = counts[e];
+  if (off < 0 || off >= R || n <= 0) return 0;
+  return n < R - off ? n : R - off;
+}
 
 // Asks for a tile to be brought into L2; completes on its own, nothing waits for it.
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
@@ -174,7 +209,7 @@ __device__ __forceinline__ TileCoord locate_tile(int tile, const int* mb_prefix,
   c.nb = local / mblocks;
   c.mb = local - c.nb * mblocks;
   c.row0 = a.offsets[lo] + static_cast<int64_t>(c.mb) * kBM;
-  const int64_t left = a.counts[lo] - static_cast<int64_t>(c.mb) * kBM;
+  const int64_t left = expert_rows(a.offsets, a.counts, a.R, lo) - static_cast<int64_t>(c.mb) * kBM;
   c.rows = static_cast<int>(left < kBM ? left : kBM);
   return c;
 }
@@ -193,14 +228,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   int* abort_flag = reinterpret_cast<int*>(tmem_base_slot + 1);
+  uint64_t* drain = reinterpret_cast<uint64_t*>(abort_flag + 1);  // see drain_on_exit
   uint4* stage = reinterpret_cast<uint4*>(smem + kStages * kStageBytes + 256);  // 4 warps x 32 rows x 128 B
   int* mb_prefix = reinterpret_cast<int*>(smem + kStages * kStageBytes + 256 + kEpiStageBytes);  // [E + 1]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int fills = 0;            // producer: stage fills issued so far
+  bool mma_issued = false;  // MMA thread: at least one MMA is (or was) in flight
 
   // ---- set-up: tile table, barriers, TMEM ----------------------------------------------
   for (int e = threadIdx.x; e < a.E; e += kGemmThreads) {
-    const int64_t n = a.counts[e];
+    const int64_t n = expert_rows(a.offsets, a.counts, a.R, e);
+    if (n != a.counts[e] && a.counts[e] > 0 && a.status != nullptr && blockIdx.x == 0)
+      atomicOr(a.status, FMOE_STATUS_BAD_EXPERT);  // rows past the end of A were cut off
     mb_prefix[e + 1] = static_cast<int>((n + kBM - 1) / kBM);
   }
   if (threadIdx.x == 0) {
@@ -214,6 +254,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       mbar_init(&tmem_full[i], 1);
       mbar_init(&tmem_empty[i], 4);
     }
+    mbar_init(drain, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -297,6 +338,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tma_load_2d(smem_b + stage * kBBytes, &map_w, kb * kBK, w_row0, &full[stage]);
           tma_load_2d(smem_b + stage * kBBytes + kBBytes / 2, &map_w, kb * kBK, w_row1, &full[stage]);
         }
+        ++fills;
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
@@ -314,6 +356,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int kb = 0; kb < a.k_blocks; ++kb) {
         if (!mbar_wait(&full[stage], phase, abort_flag, a.spin_limit)) goto timed_out;
         tcgen05_fence_after();
+        mma_issued = true;
         const uint64_t da = smem_desc(smem_u32(smem_a + stage * kABytes));
         if (a.w_transposed) {
           const uint64_t db = smem_desc_mn(smem_u32(smem_b + stage * kBBytes), kBBytes / 4);
@@ -346,7 +389,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, a.spin_limit)) goto timed_out;
       tcgen05_fence_after();
       const int row = quarter * 32 + lane;
-      const bool valid = row < c.rows;
+      const bool valid = row < c.rows && c.row0 + row < a.R;  // never past A's rows, whatever the counts say
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
       // Address of this lane's output row (0 = no row): the same row as in A, the row the map
       // names, or wherever the address table points (possibly another GPU's memory).
@@ -381,8 +424,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             uint32_t r[32];
             tmem_ld32(taddr + c0 + 32 * h, r);
             tmem_ld_wait();
+            if (a.gelu) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+              for (int i = 0; i < 32; ++i) f[i] = gelu_erf(__uint_as_float(r[i]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+            }
           }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -416,6 +464,7 @@ timed_out:
   if (a.status != nullptr) atomicOr(a.status, FMOE_STATUS_WAIT_TIMEOUT);
 
 done:
+  drain_on_exit(warp, lane, fills, mma_issued, full, drain, abort_flag, kStages, a.spin_limit);
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -438,7 +487,7 @@ struct WgradArgs {
   const int64_t* offsets;
   const int64_t* counts;
   __nv_bfloat16* grad_w;  // [E, N, K]
-  int64_t N, K;
+  int64_t N, K, R;
   int E, n_blocks, k_blocks;  // tiles per expert: N/128 x K/256
   int skip_loads;
   uint32_t spin_limit;
@@ -460,11 +509,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   int* abort_flag = reinterpret_cast<int*>(tmem_base_slot + 1);
+  uint64_t* drain = reinterpret_cast<uint64_t*>(abort_flag + 1);
   uint4* stage_buf = reinterpret_cast<uint4*>(smem + kStages * kStageBytes + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int fills = 0;
+  bool mma_issued = false;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    mbar_init(drain, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -496,7 +549,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int local = tile - e * tiles_per_expert;
       const int nb = local / a.k_blocks, kbk = local - nb * a.k_blocks;
       const int64_t row0 = a.offsets[e];
-      const int chunks = static_cast<int>((a.counts[e] + kBK - 1) / kBK);
+      const int chunks = static_cast<int>((expert_rows(a.offsets, a.counts, a.R, e) + kBK - 1) / kBK);
       for (int kb = 0; kb < chunks; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
         mbar_expect_tx(&full[stage], kStageBytes);
@@ -509,6 +562,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int piece = 0; piece < 4; ++piece)
           tma_load_2d(smem_b + stage * kBBytes + piece * (kBBytes / 4), &map_a, kbk * kBN + piece * 64, row,
                       &full[stage]);
+        ++fills;
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
@@ -519,7 +573,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     int it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int e = tile / tiles_per_expert;
-      const int64_t rows = a.counts[e];
+      const int64_t rows = expert_rows(a.offsets, a.counts, a.R, e);
       const int chunks = static_cast<int>((rows + kBK - 1) / kBK);
       if (chunks == 0) continue;  // the epilogue writes zeros for this tile on its own
       const int acc = it & 1;
@@ -532,19 +586,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!mbar_wait(&full[stage], phase, abort_flag, a.spin_limit)) goto timed_out;
         const int valid = static_cast<int>(rows - static_cast<int64_t>(kb) * kBK);
         if (valid < kBK) {
-          // rows valid..63 of this chunk belong to the next expert: clear them in the grad_c
-          // tile (each reduction row is one 128-byte line in each of the two boxes)
+          // rows valid..63 of this chunk belong to the next expert (or to nobody: the unused
+          // tail of a capacity-sized buffer, whose bytes may read as NaN or Inf): clear them in
+          // BOTH tiles, since 0 x NaN is NaN (each reduction row is one 128-byte line in each
+          // of the two grad_c boxes and the four boxes of the other operand)
           uint4* tile_g = reinterpret_cast<uint4*>(smem_a + stage * kABytes);
           const int lines = (kBK - valid) * 2;
           for (int i = lane; i < lines * 8; i += 32) {
             const int line = i >> 3, piece = line & 1, r = valid + (line >> 1);
             tile_g[piece * (kABytes / 2 / 16) + r * 8 + (i & 7)] = make_uint4(0, 0, 0, 0);
           }
+          uint4* tile_a = reinterpret_cast<uint4*>(smem_b + stage * kBBytes);
+          const int lines_a = (kBK - valid) * 4;
+          for (int i = lane; i < lines_a * 8; i += 32) {
+            const int line = i >> 3, piece = line & 3, r = valid + (line >> 2);
+            tile_a[piece * (kBBytes / 4 / 16) + r * 8 + (i & 7)] = make_uint4(0, 0, 0, 0);
+          }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor core reads
         }
         __syncwarp();
         tcgen05_fence_after();
         if (lane == 0) {
+          mma_issued = true;
           const uint64_t da = smem_desc_mn(smem_u32(smem_a + stage * kABytes), kABytes / 2);
           const uint64_t db = smem_desc_mn(smem_u32(smem_b + stage * kBBytes), kBBytes / 4);
 #pragma unroll
@@ -566,7 +629,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int e = tile / tiles_per_expert;
       const int local = tile - e * tiles_per_expert;
       const int nb = local / a.k_blocks, kbk = local - nb * a.k_blocks;
-      const bool empty_expert = a.counts[e] <= 0;
+      const bool empty_expert = expert_rows(a.offsets, a.counts, a.R, e) <= 0;
       const int row = quarter * 32 + lane;
       char* my_row = reinterpret_cast<char*>(a.grad_w + (static_cast<int64_t>(e) * a.N + nb * kBM + row) * a.K +
                                              static_cast<int64_t>(kbk) * kBN);
@@ -621,6 +684,7 @@ timed_out:
   if (a.status != nullptr) atomicOr(a.status, FMOE_STATUS_WAIT_TIMEOUT);
 
 done:
+  drain_on_exit(warp, lane, fills, mma_issued, full, drain, abort_flag, kStages, a.spin_limit);
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -688,8 +752,11 @@ using namespace fmoe;
 
 extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
                                  const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
-                                 int64_t E, int64_t R, int64_t N, int64_t K, int swiglu, int32_t* status,
+                                 int64_t E, int64_t R, int64_t N, int64_t K, int activation, int32_t* status,
                                  void* stream) {
+  FMOE_REQUIRE(activation >= FMOE_ACT_NONE && activation <= FMOE_ACT_GELU, FMOE_ERR_ARG,
+               "fmoe_grouped_gemm: activation must be FMOE_ACT_NONE, FMOE_ACT_SWIGLU or FMOE_ACT_GELU");
+  const int swiglu = activation == FMOE_ACT_SWIGLU;
   FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm: bad sizes");
   FMOE_REQUIRE(E <= kMaxExperts, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: supports E <= %d", kMaxExperts);
   FMOE_REQUIRE(K % kBK == 0, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm: K=%lld must be a multiple of %d",
@@ -728,6 +795,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   g.w_rows_per_expert = static_cast<int>(N);
   g.up_row_offset = static_cast<int>(swiglu ? N / 2 : 128);
   g.swiglu = swiglu ? 1 : 0;
+  g.gelu = activation == FMOE_ACT_GELU ? 1 : 0;
   g.w_transposed = 0;
   g.skip_loads = g_gemm_skip_loads;
   g.prefetch = prefetch_depth(R, E);
@@ -780,6 +848,7 @@ extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* 
   g.w_rows_per_expert = static_cast<int>(N);
   g.up_row_offset = 0;
   g.swiglu = 0;
+  g.gelu = 0;
   g.w_transposed = 1;
   g.skip_loads = g_gemm_skip_loads;
   g.prefetch = prefetch_depth(R, E);
@@ -825,6 +894,7 @@ extern "C" int fmoe_grouped_gemm_wgrad(const void* grad_c, const void* a, void* 
   g.grad_w = static_cast<__nv_bfloat16*>(grad_w);
   g.N = N;
   g.K = K;
+  g.R = R;
   g.E = static_cast<int>(E);
   g.n_blocks = static_cast<int>(N / kBM);
   g.k_blocks = static_cast<int>(K / kBN);

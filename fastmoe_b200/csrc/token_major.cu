@@ -614,7 +614,41 @@ __global__ void __launch_bounds__(256)
     st_stream16(dh + r * 2 * ffvec + ffvec + c, pack16<FMOE_BF16>(du));
   }
 }
+// Derivative of the exact GELU epilogue: grad_h = grad_act * (Phi(h) + h * phi(h)), Phi and phi
+// the standard normal distribution and density; streaming, fp32 arithmetic.
+__global__ void __launch_bounds__(256)
+    gelu_bwd_kernel(const uint4* __restrict__ h, const uint4* __restrict__ g, uint4* __restrict__ dh, int64_t total) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float x[8], gr[8], d[8];
+    unpack16<FMOE_BF16>(ld_stream16(h + i), x);
+    unpack16<FMOE_BF16>(ld_stream16(g + i), gr);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float cdf = 0.5f * (1.f + erff(x[k] * 0.70710678118654752f));
+      const float pdf = 0.39894228040143268f * __expf(-0.5f * x[k] * x[k]);
+      d[k] = gr[k] * (cdf + x[k] * pdf);
+    }
+    st_stream16(dh + i, pack16<FMOE_BF16>(d));
+  }
+}
 }  // namespace fmoe
+
+extern "C" int fmoe_gelu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t n,
+                             void* stream) {
+  FMOE_REQUIRE(rows >= 0 && n >= 0, FMOE_ERR_ARG, "fmoe_gelu_bwd: negative size");
+  FMOE_REQUIRE(n % 8 == 0, FMOE_ERR_UNSUPPORTED, "fmoe_gelu_bwd: n=%lld must be a multiple of 8", (long long)n);
+  if (rows == 0 || n == 0) return FMOE_OK;
+  FMOE_REQUIRE(h && grad_act && grad_h, FMOE_ERR_ARG, "fmoe_gelu_bwd: null pointer argument");
+  FMOE_REQUIRE(aligned_to(h, 16) && aligned_to(grad_act, 16) && aligned_to(grad_h, 16), FMOE_ERR_ARG,
+               "fmoe_gelu_bwd: buffers must be 16-byte aligned");
+  const int64_t total = rows * (n / 8);
+  const int64_t blocks = (total + 255) / 256;
+  const int grid = static_cast<int>(blocks < kNumSMs * 8 ? blocks : kNumSMs * 8);
+  gelu_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(h), static_cast<const uint4*>(grad_act), static_cast<uint4*>(grad_h), total);
+  return check_launch("gelu_bwd_kernel");
+}
 
 extern "C" int fmoe_swiglu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
                                void* stream) {

@@ -45,8 +45,25 @@ class _AllToAllRows(torch.autograd.Function):
 
 
 def all_to_all_rows(x, out_splits, in_splits, group=None):
-    """Row exchange with gradient. `in_splits[r]` rows go to rank r, `out_splits[r]` come from it."""
-    return _AllToAllRows.apply(x, list(out_splits), list(in_splits), group)
+    """Row exchange with gradient. `in_splits[r]` rows go to rank r, `out_splits[r]` come from it.
+
+    The split lists are checked on the host before anything is enqueued: a list of the wrong
+    length, a negative count or send counts that do not add up to the rows of `x` raise
+    ValueError here, on this rank, instead of surfacing as a mismatched collective that the
+    other ranks wait on.
+    """
+    out_splits, in_splits = [int(n) for n in out_splits], [int(n) for n in in_splits]
+    world = dist.get_world_size(group)
+    if len(in_splits) != world or len(out_splits) != world:
+        raise ValueError(
+            f"all_to_all_rows needs one send and one receive count per rank ({world}), got "
+            f"{len(in_splits)} and {len(out_splits)}"
+        )
+    if min(in_splits + out_splits, default=0) < 0:
+        raise ValueError(f"negative split size in {in_splits} / {out_splits}")
+    if sum(in_splits) != x.shape[0]:
+        raise ValueError(f"send counts {in_splits} add up to {sum(in_splits)}, but there are {x.shape[0]} rows to send")
+    return _AllToAllRows.apply(x, out_splits, in_splits, group)
 
 
 class SplitList(list):
@@ -118,29 +135,39 @@ def regroup_indices(counts_by_source, device, host_counts=None):
 def fused_layout(C: torch.Tensor, rank: int, cap_rows: int, row_bytes: int):
     """Placement arithmetic of the fused (peer-store) exchange, from everybody's per-expert
     counts C[s, e] (rows that rank s routes to global expert e; experts sharded contiguously).
+    The statement in tensor operations of what `fmoe_ep_layout` computes on the GPU in two
+    small launches: the CUDA path is checked against it, and CPU tests emulate the exchange
+    with it.
 
     Every rank lays out what it receives expert-major, sources in rank order inside an expert.
-    Returns, all on C's device and with sizes that do not depend on the data:
+    Rows that would land at or beyond `cap_rows` do not exist: their senders drop them, and the
+    counts the experts see stop there. Returns, all on C's device and with sizes that do not
+    depend on the data:
       dst_row0       int64 [E]         row on expert e's owner where THIS rank's rows for e begin
-      counts_local   int64 [E_local]   rows this rank receives per local expert
-      offsets_local  int64 [E_local]   their exclusive prefix sum
+      counts_local   int64 [E_local]   rows this rank receives per local expert (cut off at cap_rows)
+      offsets_local  int64 [E_local]   their first rows
       src_rank       int64 [cap_rows]  source rank of every receive-buffer row
       origin_byte    int64 [cap_rows]  byte offset, in the source's sorted-slot buffer, of the slot the
-                                       row came from (entries past the received total are meaningless)
+                                       row came from (entries from rows_used on are meaningless)
+      rows_used      int64 [1]         rows of the receive buffer in use
     """
     world, E = C.shape
     el = E // world
+    C = C.clamp(min=0)
     per_dest = C.view(world, world, el).permute(1, 2, 0).reshape(world, el * world)  # [d, (e, s)]
     seg_start = torch.cumsum(per_dest, 1) - per_dest
     # contiguous: the kernel indexes it by global expert
     dst_row0 = seg_start.view(world, el, world)[:, :, rank].reshape(E).contiguous()
     mine = per_dest[rank]  # sizes of the (e, s) segments this rank receives
-    counts_local = mine.view(el, world).sum(1).contiguous()
-    offsets_local = (torch.cumsum(counts_local, 0) - counts_local).contiguous()
+    received = mine.view(el, world).sum(1)
+    first = torch.cumsum(received, 0) - received
+    counts_local = torch.minimum(received, (cap_rows - first).clamp(min=0)).contiguous()
+    offsets_local = first.clamp(max=cap_rows).contiguous()
+    rows_used = received.sum().clamp(max=cap_rows).reshape(1)
     rows = torch.arange(cap_rows, device=C.device)
     my_start = seg_start[rank]
     seg = torch.searchsorted(my_start + mine, rows, right=True).clamp_(max=el * world - 1)
     src_rank = seg % world
     origin_offsets = torch.cumsum(C, 1) - C  # [s, e]: start of expert e in rank s's sorted rows
     origin_slot = origin_offsets[src_rank, rank * el + seg // world] + (rows - my_start[seg])
-    return dst_row0, counts_local, offsets_local, src_rank, (origin_slot * row_bytes).contiguous()
+    return dst_row0, counts_local, offsets_local, src_rank, (origin_slot * row_bytes).contiguous(), rows_used

@@ -2,23 +2,27 @@
 
 `grouped_gemm` multiplies every expert's contiguous block of rows by that expert's
 weight matrix in ONE persistent launch, reading the per-expert row ranges from device
-memory, and `grouped_swiglu_ffn` chains two of them into down(silu(gate(x)) * up(x)).
-They replace the Python loop over `self.experts` in `MoEFeedForward.compute_experts` of
-polkadot21/fastmoe (src/fastmoe/models/tiny_model.py:282-294).
+memory. `grouped_swiglu_ffn` chains two of them into down(silu(gate(x)) * up(x)) and
+`grouped_gelu_ffn` into fc2(gelu(fc1(x))), the reference's own expert
+(src/fastmoe/models/tiny_model.py:68-77). They replace the Python loop over `self.experts`
+in `MoEFeedForward.compute_experts` of polkadot21/fastmoe (tiny_model.py:282-294).
 
 Forward, data gradient and weight gradient all run on the hand-written tcgen05 kernels
 (`csrc/grouped_gemm.cu`) with the per-expert row ranges read from device memory; the
-SwiGLU derivative between them is one streaming kernel over recomputed pre-activations.
-Shapes the kernels do not tile (N or K not a multiple of 64/128/256) fall back to
-per-expert library products.
+activation's derivative between them is one streaming kernel over recomputed
+pre-activations. Shapes the kernels do not tile raise ValueError, forward and backward
+alike: there is no library fallback.
 """
 
 from __future__ import annotations
 
 import torch
 
+from .. import _lib
 from . import ops
 from .ops import _require_cuda, _status_word, _stream_ptr
+
+ACT_NONE, ACT_SWIGLU, ACT_GELU = _lib.ACT_NONE, _lib.ACT_SWIGLU, _lib.ACT_GELU
 
 
 def _check(a, w, offsets, counts):
@@ -33,13 +37,51 @@ def _check(a, w, offsets, counts):
         raise ValueError("offsets and counts need one entry per expert")
 
 
-def _launch(a, w, offsets, counts, swiglu, row_map=None, covers_all_rows=False, row_ptrs=None):
+def check_shapes(N: int, K: int, act: int = ACT_NONE, training: bool = False):
+    """Raises ValueError unless the kernels tile a [*, K] x [E, N, K] product (and, with
+    `training`, its two gradients): the forward needs K % 64 == 0 and N % 256 == 0, the
+    gradients K % 256 == 0 and N % 128 == 0."""
+    if K % 64 or N % 256:
+        raise ValueError(f"grouped_gemm needs K a multiple of 64 and N a multiple of 256, got K={K}, N={N}")
+    if training and (K % 256 or N % 128):
+        raise ValueError(f"the grouped GEMM's gradients need K a multiple of 256 and N of 128, got K={K}, N={N}")
+    if act == ACT_SWIGLU and (N // 2) % 128:
+        raise ValueError(f"SwiGLU needs N = 2*ff with ff a multiple of 128, got N={N}")
+
+
+def supported(N: int, K: int, act: int = ACT_NONE, training: bool = False) -> bool:
+    try:
+        check_shapes(N, K, act, training)
+    except ValueError:
+        return False
+    return True
+
+
+def _after_launch(device, what):
+    """With checking switched on (FASTMOE_B200_CHECK=1) reads the status word after the launch
+    and raises if a bounded device-side wait gave up or rows were cut off."""
+    if ops._check:
+        value = ops.read_status(device)
+        if value:
+            raise RuntimeError(f"{what}: device status word = {value}"
+                               + (" (a bounded wait gave up)" if value & _lib.STATUS_WAIT_TIMEOUT else ""))  # fmt: skip
+
+
+def _launch(a, w, offsets, counts, act, row_map=None, covers_all_rows=False, row_ptrs=None, out=None):
+    """One grouped GEMM launch. `act` is ACT_NONE / ACT_SWIGLU / ACT_GELU (False / True also
+    mean the first two). `out` ([R, cols], bf16, contiguous) receives the result instead of a
+    fresh tensor; with `row_ptrs` every row goes where its table entry points."""
     a, w = a.contiguous(), w.contiguous()
+    act = int(act)
     R, K = a.shape
     E, N, _ = w.shape
-    cols = N // 2 if swiglu else N
+    cols = N // 2 if act == ACT_SWIGLU else N
     if row_ptrs is not None:
         c = None  # every row goes where its table entry points
+    elif out is not None:
+        if out.shape != (R, cols) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+            raise ValueError(f"out must be a contiguous bfloat16 [{R}, {cols}] tensor")
+        c = out
     elif covers_all_rows or R == 0:
         c = torch.empty(R, cols, dtype=torch.bfloat16, device=a.device)
     else:  # rows that belong to no expert are never written: start from zeros so they are defined
@@ -48,20 +90,23 @@ def _launch(a, w, offsets, counts, swiglu, row_map=None, covers_all_rows=False, 
         "fmoe_grouped_gemm", 1, a.data_ptr(), w.data_ptr(), c.data_ptr() if c is not None else None,
         offsets.data_ptr(), counts.data_ptr(), row_map.data_ptr() if row_map is not None else None,
         row_ptrs.data_ptr() if row_ptrs is not None else None, E, R, N, K,
-        1 if swiglu else 0, _status_word(a.device).data_ptr(), _stream_ptr(a.device),
+        act, _status_word(a.device).data_ptr(), _stream_ptr(a.device),
     )  # fmt: skip
+    _after_launch(a.device, "fmoe_grouped_gemm")
     return c
 
 
 class _GroupedGemm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, a, w, offsets, counts, swiglu, row_map, covers_all_rows):
+    def forward(ctx, a, w, offsets, counts, act, row_map, covers_all_rows):
         _check(a, w, offsets, counts)
         if row_map is not None and (row_map.dtype != torch.int64 or row_map.numel() != a.shape[0]):
             raise ValueError("row_map must be an int64 device tensor with one entry per row of a")
+        training = any(ctx.needs_input_grad[:2])
+        check_shapes(w.shape[1], w.shape[2], act, training)
         ctx.save_for_backward(a, w, offsets, counts, row_map)
-        ctx.swiglu, ctx.covers_all_rows = swiglu, covers_all_rows
-        return _launch(a, w, offsets, counts, swiglu, row_map, covers_all_rows)
+        ctx.act, ctx.covers_all_rows = act, covers_all_rows
+        return _launch(a, w, offsets, counts, act, row_map, covers_all_rows)
 
     @staticmethod
     def backward(ctx, grad_c):
@@ -69,13 +114,16 @@ class _GroupedGemm(torch.autograd.Function):
         if row_map is not None:
             grad_c = grad_c.index_select(0, row_map)  # back to the row order of `a`
         grad_c = grad_c.contiguous()
-        if ctx.swiglu:
-            # recompute the pre-activations with the plain kernel, then the SwiGLU derivative
-            ff = w.shape[1] // 2
-            h = _launch(a, w, offsets, counts, False, covers_all_rows=ctx.covers_all_rows)
+        if ctx.act != ACT_NONE:
+            # recompute the pre-activations with the plain kernel, then the activation's derivative
+            h = _launch(a, w, offsets, counts, ACT_NONE, covers_all_rows=ctx.covers_all_rows)
             grad_h = torch.empty_like(h)
-            ops._call("fmoe_swiglu_bwd", 1, h.data_ptr(), grad_c.data_ptr(), grad_h.data_ptr(), h.shape[0], ff,
-                      _stream_ptr(h.device))  # fmt: skip
+            if ctx.act == ACT_SWIGLU:
+                ops._call("fmoe_swiglu_bwd", 1, h.data_ptr(), grad_c.data_ptr(), grad_h.data_ptr(), h.shape[0],
+                          w.shape[1] // 2, _stream_ptr(h.device))  # fmt: skip
+            else:
+                ops._call("fmoe_gelu_bwd", 1, h.data_ptr(), grad_c.data_ptr(), grad_h.data_ptr(), h.shape[0],
+                          w.shape[1], _stream_ptr(h.device))  # fmt: skip
             grad_c = grad_h
             del h
         need_a, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
@@ -90,8 +138,8 @@ def _dgrad(grad_c, w, offsets, counts, covers_all_rows=False, row_ptrs=None):
     its entry points and nothing is returned."""
     R, N = grad_c.shape
     E, _, K = w.shape
-    if row_ptrs is None and (N % 64 or K % 256):
-        return _dgrad_library(grad_c, w, offsets, counts)
+    if N % 64 or K % 256:
+        raise ValueError(f"the grouped GEMM's data gradient needs N a multiple of 64 and K of 256, got N={N}, K={K}")
     grad_a = None
     if row_ptrs is None:
         alloc = torch.empty if covers_all_rows else torch.zeros
@@ -102,6 +150,7 @@ def _dgrad(grad_c, w, offsets, counts, covers_all_rows=False, row_ptrs=None):
         row_ptrs.data_ptr() if row_ptrs is not None else None, E, R, N, K,
         _status_word(grad_c.device).data_ptr(), _stream_ptr(grad_c.device),
     )  # fmt: skip
+    _after_launch(grad_c.device, "fmoe_grouped_gemm_dgrad")
     return grad_a
 
 
@@ -110,50 +159,43 @@ def _wgrad(grad_c, a, w_shape, offsets, counts):
     E, N, K = w_shape
     R = a.shape[0]
     if N % 128 or K % 256:
-        return _wgrad_library(grad_c, a, w_shape, offsets, counts)
+        raise ValueError(f"the grouped GEMM's weight gradient needs N a multiple of 128 and K of 256, got N={N}, K={K}")
     grad_w = torch.empty(E, N, K, dtype=torch.bfloat16, device=a.device)
     ops._call(
         "fmoe_grouped_gemm_wgrad", 1, grad_c.data_ptr(), a.contiguous().data_ptr(), grad_w.data_ptr(),
         offsets.data_ptr(), counts.data_ptr(), E, R, N, K, _status_word(a.device).data_ptr(), _stream_ptr(a.device),
     )  # fmt: skip
+    _after_launch(a.device, "fmoe_grouped_gemm_wgrad")
     return grad_w
 
 
-def _dgrad_library(grad_c, w, offsets, counts):
-    """Shapes the kernels do not tile: per-expert library products (needs the counts on the host)."""
-    grad_a = torch.zeros(grad_c.shape[0], w.shape[2], dtype=grad_c.dtype, device=grad_c.device)
-    for e, (o, n) in enumerate(zip(offsets.tolist(), counts.tolist())):
-        if n:
-            grad_a[o : o + n] = grad_c[o : o + n] @ w[e]
-    return grad_a
-
-
-def _wgrad_library(grad_c, a, w_shape, offsets, counts):
-    grad_w = torch.zeros(w_shape, dtype=a.dtype, device=a.device)
-    for e, (o, n) in enumerate(zip(offsets.tolist(), counts.tolist())):
-        if n:
-            grad_w[e] = grad_c[o : o + n].t() @ a[o : o + n]
-    return grad_w
-
-
-def grouped_gemm(a, w, offsets, counts, swiglu=False, row_map=None, covers_all_rows=False):
-    """C[rows of e] = A[rows of e] @ w[e].T (or the fused SwiGLU of its two halves).
+def grouped_gemm(a, w, offsets, counts, swiglu=False, row_map=None, covers_all_rows=False, activation=None):
+    """C[rows of e] = A[rows of e] @ w[e].T, optionally followed by an activation in the epilogue.
 
     a [R, K] bf16; w [E, N, K] bf16; offsets, counts int64 [E] on the device (rows
-    [offsets[e], offsets[e]+counts[e]) belong to expert e). Returns bf16 [R, N] (or [R, N/2]).
-    `row_map` (int64 [R], a permutation) stores the result of row r at row row_map[r].
-    `covers_all_rows=True` promises that every row belongs to an expert, which saves the
-    zero-fill of the output.
+    [offsets[e], offsets[e]+counts[e]) belong to expert e). Returns bf16 [R, N] (or [R, N/2]
+    for SwiGLU, which pairs the first N/2 weight rows as gate with the last N/2 as up).
+    `activation`: ACT_NONE, ACT_SWIGLU or ACT_GELU (`swiglu=True` is the older spelling of
+    ACT_SWIGLU). `row_map` (int64 [R], a permutation) stores the result of row r at row
+    row_map[r]. `covers_all_rows=True` promises that every row belongs to an expert, which
+    saves the zero-fill of the output.
     """
-    return _GroupedGemm.apply(a, w, offsets, counts, bool(swiglu), row_map, bool(covers_all_rows))
+    act = int(activation) if activation is not None else (ACT_SWIGLU if swiglu else ACT_NONE)
+    return _GroupedGemm.apply(a, w, offsets, counts, act, row_map, bool(covers_all_rows))
 
 
 def grouped_swiglu_ffn(x, w_gate_up, w_down, offsets, counts, row_map=None, covers_all_rows=False):
     """down(silu(gate(x)) * up(x)) per expert. w_gate_up [E, 2*ff, D] (gate rows first), w_down [E, D, ff].
     `row_map` reorders the rows of the result (see grouped_gemm)."""
-    hidden = grouped_gemm(x, w_gate_up, offsets, counts, swiglu=True, covers_all_rows=covers_all_rows)
-    return grouped_gemm(hidden, w_down, offsets, counts, swiglu=False, row_map=row_map,
-                        covers_all_rows=covers_all_rows)  # fmt: skip
+    hidden = grouped_gemm(x, w_gate_up, offsets, counts, activation=ACT_SWIGLU, covers_all_rows=covers_all_rows)
+    return grouped_gemm(hidden, w_down, offsets, counts, row_map=row_map, covers_all_rows=covers_all_rows)
+
+
+def grouped_gelu_ffn(x, w1, w2, offsets, counts, row_map=None, covers_all_rows=False):
+    """fc2(gelu(fc1(x))) per expert, bias-free: the reference's expert (tiny_model.py:68-77).
+    w1 [E, ff, D], w2 [E, D, ff], both in nn.Linear layout."""
+    hidden = grouped_gemm(x, w1, offsets, counts, activation=ACT_GELU, covers_all_rows=covers_all_rows)
+    return grouped_gemm(hidden, w2, offsets, counts, row_map=row_map, covers_all_rows=covers_all_rows)
 
 
 def grouped_gemm_to_rows(a, w, offsets, counts, row_ptrs):
@@ -162,4 +204,4 @@ def grouped_gemm_to_rows(a, w, offsets, counts, row_ptrs):
     _check(a, w, offsets, counts)
     if row_ptrs.dtype != torch.int64 or row_ptrs.numel() < a.shape[0]:
         raise ValueError("row_ptrs must be an int64 device tensor with one entry per row of a")
-    _launch(a, w, offsets, counts, False, row_ptrs=row_ptrs)
+    _launch(a, w, offsets, counts, ACT_NONE, row_ptrs=row_ptrs)

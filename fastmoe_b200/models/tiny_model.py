@@ -14,7 +14,10 @@ unpermute, tiny_model.py:42-420). What differs, on purpose:
   * FAST `forward` hands the per-expert outputs to the grouped combine as separate
     tensors: no torch.cat of expert results;
   * `expert_type="swiglu"` gives bias-free SwiGLU experts (gate/up/down) instead of
-    Linear-GELU-Linear.
+    Linear-GELU-Linear;
+  * in bf16 with the FAST implementation both expert types run as two grouped tcgen05 GEMM
+    launches (activation fused in the first one's epilogue) instead of a Python loop of
+    per-expert library calls.
 
 There is no CPU path: inputs must live on a CUDA device.
 """
@@ -28,8 +31,9 @@ import torch.nn.functional as F
 from torch.profiler import record_function
 
 from .. import consts, exchange
+from ..kernels import experts as expert_kernels
 from ..kernels import routing
-from ..kernels.experts import grouped_swiglu_ffn
+from ..kernels.experts import grouped_gelu_ffn, grouped_swiglu_ffn
 from ..kernels.ops import grouped_weighted_scatter_add
 
 
@@ -154,7 +158,7 @@ class MoEFeedForward(nn.Module):
         if self.num_local_experts > 1:
             to_expert_major, to_rank_major, _ = exchange.regroup_indices(recv_counts, recv.device, nested)
             splits.to_expert_major, splits.to_rank_major = to_expert_major, to_rank_major
-            tokens_per_expert.to_expert_major = to_expert_major
+            tokens_per_expert.to_expert_major, tokens_per_expert.to_rank_major = to_expert_major, to_rank_major
             recv = recv.index_select(0, to_expert_major)
         return recv, splits, send_list, tokens_per_expert
 
@@ -212,30 +216,63 @@ class MoEFeedForward(nn.Module):
             outs.append(expert(chunk) if chunk.shape[0] > 0 else chunk.new_empty(0, self.dim))
         return outs
 
-    def _grouped_ffn(self, recv_data, tokens_per_expert):
-        """SwiGLU experts on the FAST path: two grouped-GEMM launches, no per-expert loop."""
+    def _grouped_ffn(self, recv_data, tokens_per_expert, arrival_order_out=False):
+        """Experts on the FAST path in bf16: two grouped-GEMM launches, no per-expert loop.
+        With `arrival_order_out` (several ranks, rows regrouped by expert on arrival) the second
+        GEMM's epilogue stores every result row at its ARRIVAL position, so that the return
+        exchange needs no reordering copy."""
         counts = getattr(tokens_per_expert, "device_counts", None)
         if counts is None:
             staging = torch.tensor(list(tokens_per_expert), dtype=torch.int64, pin_memory=True)
             counts = staging.to(recv_data.device, non_blocking=True)
         offsets = torch.cumsum(counts, 0) - counts
-        # with several ranks the rows arrived ordered by source rank and were regrouped by
-        # expert; the down-projection's epilogue stores them straight back in arrival order
-        row_map = getattr(tokens_per_expert, "to_expert_major", None)
-        out = self.experts(recv_data, offsets, counts, row_map)
-        out.fmoe_rank_major = row_map is not None
-        return out
+        row_map = getattr(tokens_per_expert, "to_expert_major", None) if arrival_order_out else None
+        if self.expert_type == "swiglu":
+            return self.experts(recv_data, offsets, counts, row_map)
+        # the reference's experts (nn.ModuleList of Linear-GELU-Linear, tiny_model.py:68-77): their
+        # weights are stacked into the [E, N, K] layout the grouped GEMM reads; gradients flow
+        # back to the individual modules through the stack
+        w1 = torch.stack([expert[0].weight for expert in self.experts])
+        w2 = torch.stack([expert[2].weight for expert in self.experts])
+        if w1.dtype != torch.bfloat16:  # bf16 autocast over fp32 modules: cast as autocast's linear would
+            recv_data, w1, w2 = recv_data.bfloat16(), w1.bfloat16(), w2.bfloat16()
+        return grouped_gelu_ffn(recv_data, w1, w2, offsets, counts, row_map, covers_all_rows=True)
+
+    @staticmethod
+    def _autocast_bf16():
+        return torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
 
     def _use_grouped(self, recv_data):
-        return (self.expert_type == "swiglu" and self.implementation == consts.MoEImplementation.FAST
-                and recv_data.dtype == torch.bfloat16)  # fmt: skip
+        if self.implementation != consts.MoEImplementation.FAST or not recv_data.is_cuda:
+            return False
+        if self.expert_type == "swiglu":
+            return recv_data.dtype == torch.bfloat16
+        # GELU experts: bf16 modules and rows, or any under bf16 autocast, and only widths the
+        # kernels tile (forward and, when training, backward); everything else keeps the
+        # per-expert modules, exactly as the reference runs them
+        fc1 = self.experts[0][0].weight
+        in_bf16 = fc1.dtype == torch.bfloat16 and recv_data.dtype == torch.bfloat16
+        if not fc1.is_cuda or not (in_bf16 or self._autocast_bf16()):
+            return False
+        ff, dim = fc1.shape
+        training = torch.is_grad_enabled() and (fc1.requires_grad or recv_data.requires_grad)
+        return (expert_kernels.supported(ff, dim, expert_kernels.ACT_GELU, training)
+                and expert_kernels.supported(dim, ff, expert_kernels.ACT_NONE, training))  # fmt: skip
 
-    def compute_experts(self, recv_data, tokens_per_expert):
-        """Concatenated expert outputs, rows in the order of recv_data (tiny_model.py:282-294)."""
+    def compute_experts(self, recv_data, tokens_per_expert, arrival_order_out=False):
+        """Concatenated expert outputs, rows in the order of recv_data (tiny_model.py:282-294).
+
+        `arrival_order_out=True` (used by `forward` and the pipelined schedule together with
+        `combine_exchange(..., rows_in_arrival_order=True)`) returns the rows in the order they
+        ARRIVED from the other ranks instead, where that saves a copy; both calls must agree."""
         if self._use_grouped(recv_data):
-            return self._grouped_ffn(recv_data, tokens_per_expert)
+            return self._grouped_ffn(recv_data, tokens_per_expert, arrival_order_out)
         outs = self.expert_outputs(recv_data, tokens_per_expert)
-        return torch.cat(outs, dim=0) if outs else recv_data.new_empty(0, self.dim)
+        out = torch.cat(outs, dim=0) if outs else recv_data.new_empty(0, self.dim)
+        to_rank_major = getattr(tokens_per_expert, "to_rank_major", None)
+        if arrival_order_out and to_rank_major is not None:
+            out = out.index_select(0, to_rank_major)
+        return out
 
     def compute_experts_static(self, recv_data):
         """Experts over equal shares of the rows (tiny_model.py:296-306): local expert e gets
@@ -246,13 +283,15 @@ class MoEFeedForward(nn.Module):
         return self.compute_experts(recv_data, shares)
 
     # -- stage 4 ---------------------------------------------------------------------------
-    def combine_exchange(self, expert_output, recv_splits, send_splits):
-        """Returns expert outputs to the ranks that own the tokens (tiny_model.py:308-339)."""
+    def combine_exchange(self, expert_output, recv_splits, send_splits, rows_in_arrival_order=False):
+        """Returns expert outputs to the ranks that own the tokens (tiny_model.py:308-339).
+        `expert_output` has the row order of what `dispatch_exchange` returned (grouped by local
+        expert) unless `rows_in_arrival_order` says that `compute_experts` already put the rows
+        back in the order they arrived in (see there)."""
         if self.world_size == 1:
             return expert_output
         to_rank_major = getattr(recv_splits, "to_rank_major", None)
-        already = getattr(expert_output, "fmoe_rank_major", False)
-        if to_rank_major is not None and self.num_local_experts > 1 and not already:
+        if to_rank_major is not None and self.num_local_experts > 1 and not rows_in_arrival_order:
             expert_output = expert_output.index_select(0, to_rank_major)
         return exchange.all_to_all_rows(expert_output, list(send_splits), list(recv_splits), self.group)
 
@@ -272,21 +311,32 @@ class MoEFeedForward(nn.Module):
             return out.view(B, T, D)
         raise NotImplementedError
 
-    def enable_fused_exchange(self, max_tokens, capacity_factor=2.0):
-        """With several ranks and SwiGLU experts: lets gradient-free bf16 forwards of up to
-        `max_tokens` tokens run with the exchange fused into the permute kernel and the GEMM
-        epilogue (peer stores over NVLink, no all-to-all, no host synchronisation; see
-        fastmoe_b200/ep_fused.py). Collective: every rank of the group must call it."""
+    def enable_fused_exchange(self, max_tokens, capacity_factor=2.0, expert_groups=None):
+        """With several ranks and SwiGLU experts: from now on EVERY `forward` of this module,
+        with or without gradients, runs with the exchange fused into the permute kernel and
+        the GEMM epilogue (peer stores over NVLink, no all-to-all, no host synchronisation; see
+        fastmoe_b200/ep_fused.py). Collective: every rank of the group must call it, and from
+        then on all ranks take the same path by construction: the choice is made here, once,
+        not per call from rank-local conditions. A call the fused path cannot serve (more than
+        `max_tokens` tokens, a dtype other than bfloat16) raises ValueError on the rank that
+        makes it instead of silently falling back to the all-to-all path, whose collectives
+        the other ranks would not match. `disable_fused_exchange()` returns to the NCCL path
+        (again on every rank)."""
         from ..ep_fused import FusedExpertParallel
 
-        self._fused_exchange = FusedExpertParallel(self, max_tokens, capacity_factor, self.group)
+        self._fused_exchange = FusedExpertParallel(self, max_tokens, capacity_factor, self.group, expert_groups)
+        return self
+
+    def disable_fused_exchange(self):
+        self._fused_exchange = None
         return self
 
     def forward(self, x):
         fused = getattr(self, "_fused_exchange", None)
-        if (fused is not None and not torch.is_grad_enabled() and x.dtype == torch.bfloat16
-                and x.shape[0] * x.shape[1] * self.top_k <= fused.max_rows):  # fmt: skip
-            return fused(x)
+        if fused is not None:
+            needs_grad = torch.is_grad_enabled() and (
+                x.requires_grad or any(p.requires_grad for p in self.parameters()))  # fmt: skip
+            return fused.forward_with_grad(x) if needs_grad else fused(x)
         permuted, send_rank_counts, send_exp_counts, rev_idx, weights, shape = self.gate_and_sort(x)
         recv, recv_splits, send_splits, tokens_per_expert = self.dispatch_exchange(
             permuted, send_rank_counts, send_exp_counts
@@ -295,8 +345,8 @@ class MoEFeedForward(nn.Module):
                 and not self._use_grouped(recv)):  # fmt: skip
             # "no-cat": the combine reads the disjoint expert outputs through its pointer table
             return self.unpermute(self.expert_outputs(recv, tokens_per_expert), rev_idx, weights, shape)
-        expert_out = self.compute_experts(recv, tokens_per_expert)
-        final = self.combine_exchange(expert_out, recv_splits, send_splits)
+        expert_out = self.compute_experts(recv, tokens_per_expert, arrival_order_out=True)
+        final = self.combine_exchange(expert_out, recv_splits, send_splits, rows_in_arrival_order=True)
         return self.unpermute(final, rev_idx, weights, shape)
 
 
@@ -445,11 +495,11 @@ def pipelined_moe_forward(moe, inputs, streams):
                 # finish later than either alone and delay the return exchange they feed
                 streams[i].wait_event(experts_done)
             with record_function(f"S{i}: Experts {i}"):
-                eo = moe.compute_experts(recv, tokens)
+                eo = moe.compute_experts(recv, tokens, arrival_order_out=True)
             experts_done = torch.cuda.Event()
             experts_done.record()
             with record_function(f"S{i}: Combine {i}"):
-                fd = moe.combine_exchange(eo, recv_splits, send_splits)
+                fd = moe.combine_exchange(eo, recv_splits, send_splits, rows_in_arrival_order=True)
             with record_function(f"S{i}: Finalize {i}"):
                 outs[i] = moe.unpermute(fd, rev, w, shape)
         gated[i] = dispatched[i] = None

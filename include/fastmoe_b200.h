@@ -233,26 +233,81 @@ int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_of, void* gr
  *   written to (char*)peer_bases[dest GPU] + dest row * D * sizeof(element)
  * dst_row0, local_offsets int64[E]; peer_bases int64[world] (device array of mapped base
  * addresses, own buffer included); rows at or beyond cap_rows are dropped and flagged with
- * FMOE_STATUS_BAD_INDEX. The caller orders the consumers after all writers (a barrier).
+ * FMOE_STATUS_BAD_INDEX. ret_local (optional) is this GPU's own return buffer [T*K, D], one
+ * row per sorted slot, which the experts' GPUs fill later: the row of a dropped copy is
+ * zeroed in it, since nobody will send a result for it, so that the combine adds zero for
+ * that copy rather than what an earlier call left in the buffer (the reference's fixed-size
+ * exchange hands such rows "garbage", tiny_model.py:360-367). The caller orders the
+ * consumers after all writers (a barrier).
  */
 int fmoe_permute_peer_fwd(const void* x, int64_t x_row_stride, const int64_t* topk_idx,
                           const int32_t* slot_of, const int64_t* local_offsets,
                           const int64_t* dst_row0, const int64_t* peer_bases, int64_t T, int64_t K,
-                          int64_t D, int64_t E, int64_t experts_per_rank, int64_t cap_rows, int dtype,
+                          int64_t D, int64_t E, int64_t experts_per_rank, int64_t cap_rows,
+                          void* ret_local, int64_t local_lo, int64_t local_hi, int dtype,
                           int32_t* status, void* stream);
+/* local_lo, local_hi: only the copies for experts whose index on their owning GPU
+ * (expert % experts_per_rank) lies in [local_lo, local_hi) are sent; 0 and experts_per_rank
+ * send everything. Sending group after group lets the experts of one group compute while the
+ * rows of the next are still crossing NVLink: the overlap that the reference builds from token
+ * micro-batches on two streams (tiny_model.py:506-630), without thinning the rows per expert. */
+
+/*
+ * Barrier between the GPUs that share the exchange buffers, as one tiny kernel on `stream`:
+ * work enqueued after it on any rank's stream starts only when every rank's work enqueued
+ * before it (peer stores included) is complete and visible. flag_bases int64[world] (device)
+ * holds, for every rank, the mapped address of that rank's flag array (int32[world], zeroed
+ * once before the first barrier); seq is the number of this barrier, the same on all ranks,
+ * starting at 1 and growing by one per call. Takes the place of the dist.barrier / blocking
+ * collectives that order the reference's exchanges (tiny_model.py:182, :195, :210). The wait
+ * is bounded: a rank that does not arrive within timeout_ms sets FMOE_STATUS_WAIT_TIMEOUT
+ * in `status` and the kernel returns, so a missing peer never hangs the GPU.
+ */
+int fmoe_peer_barrier(const int64_t* flag_bases, int64_t world, int64_t rank, int32_t seq,
+                      int64_t timeout_ms, int32_t* status, void* stream);
+
+/*
+ * Placement arithmetic of that exchange, on the device: from the all-gathered counts
+ * counts_all[s * E + g] (rows that rank s routes to global expert g; E/world experts per
+ * rank, contiguous) it writes, for rank `rank`:
+ *   dst_row0[g]       int64[E]        row on expert g's owner where THIS rank's rows for g begin
+ *   counts_local[e]   int64[E/world]  rows this rank's expert e receives, cut off at cap_rows
+ *   offsets_local[e]  int64[E/world]  their first rows (expert-major, sources in rank order)
+ *   rows_used         int64[1]        rows of the receive buffer in use (<= cap_rows)
+ *   row_ptrs[i]       int64[cap_rows] ret_bases[source rank of row i] + row_bytes * (sorted slot
+ *                                     the row came from): where the result of receive row i goes
+ *                                     (fmoe_grouped_gemm's c_row_ptrs); 0 beyond rows_used
+ *   grad_row_ptrs     optional, the same from grad_ret_bases (the gradients' return trip)
+ * It stands for the two count exchanges and the host-side split arithmetic of
+ * MoEFeedForward.dispatch_exchange (src/fastmoe/models/tiny_model.py:176-208), without the
+ * two device-to-host reads (:187, :198-199). When more than cap_rows rows are routed to this
+ * rank, FMOE_STATUS_BAD_INDEX is set. scratch: 2*E int64. E <= 1024. Two small launches.
+ */
+int fmoe_ep_layout(const int64_t* counts_all, int64_t world, int64_t E, int64_t rank, int64_t cap_rows,
+                   int64_t row_bytes, const int64_t* ret_bases, const int64_t* grad_ret_bases,
+                   int64_t* dst_row0, int64_t* counts_local, int64_t* offsets_local, int64_t* rows_used,
+                   int64_t* row_ptrs, int64_t* grad_row_ptrs, int64_t* scratch, int32_t* status,
+                   void* stream);
 
 /* ---- expert FFN: grouped GEMM on tcgen05 ------------------------------------------ */
+/* what the epilogue applies to the product before the one rounding to bf16 */
+#define FMOE_ACT_NONE 0
+#define FMOE_ACT_SWIGLU 1 /* silu(gate half) * (up half): the output has N/2 columns */
+#define FMOE_ACT_GELU 2   /* exact GELU, 0.5 x (1 + erf(x / sqrt 2)), as torch.nn.GELU() */
 /*
  * For every expert e with rows [offsets[e], offsets[e] + counts[e]) of A:
- *   swiglu = 0:  C[rows, :N]   = A[rows, :K] x W[e]^T                       W[e] is [N, K]
- *   swiglu = 1:  C[rows, :N/2] = silu(A x Wg[e]^T) * (A x Wu[e]^T)          W[e] = [Wg; Wu], each [N/2, K]
+ *   FMOE_ACT_NONE:    C[rows, :N]   = A[rows, :K] x W[e]^T                  W[e] is [N, K]
+ *   FMOE_ACT_GELU:    C[rows, :N]   = gelu(A[rows, :K] x W[e]^T)
+ *   FMOE_ACT_SWIGLU:  C[rows, :N/2] = silu(A x Wg[e]^T) * (A x Wu[e]^T)     W[e] = [Wg; Wu], each [N/2, K]
  * A [R, K], W [E, N, K], C bf16 row-major; offsets/counts int64[E] ON THE DEVICE (the index
  * builder's output: the host never learns the counts). fp32 accumulation in tensor
  * memory, one rounding to bf16. K must be a multiple of 64, N of 256, E <= 1024.
  * Replaces the per-expert Python loop of cuBLAS GEMMs in MoEFeedForward.compute_experts
  * (src/fastmoe/models/tiny_model.py:282-294; the reference's experts are
- * Linear-GELU-Linear, tiny_model.py:68-77; SwiGLU is what the expert-parallel benchmark
- * configuration asks for). Rows of A outside every expert's range are not touched in C.
+ * Linear-GELU-Linear, tiny_model.py:68-77: one FMOE_ACT_GELU call and one FMOE_ACT_NONE call;
+ * SwiGLU is what the expert-parallel benchmark configuration asks for). Rows of A outside
+ * every expert's range are not touched in C. An expert whose range runs past row R of A is
+ * cut off at R (and FMOE_STATUS_BAD_EXPERT is set): no tile reads or writes beyond A's rows.
  * c_row_map (optional int64[R] on the device, NULL = identity) sends the result of A's row
  * r to row c_row_map[r] of C: the return-trip reordering of the expert-parallel layer
  * (expert-major rows back to source-rank-major) happens in the store, not in a copy.
@@ -264,7 +319,7 @@ int fmoe_permute_peer_fwd(const void* x, int64_t x_row_stride, const int64_t* to
  */
 int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
                       const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
-                      int64_t E, int64_t R, int64_t N, int64_t K, int swiglu, int32_t* status,
+                      int64_t E, int64_t R, int64_t N, int64_t K, int activation, int32_t* status,
                       void* stream);
 
 /*
@@ -306,6 +361,13 @@ int fmoe_swiglu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t r
  * by the fused expert-parallel exchange, whose receive buffers are sized for the worst case. */
 int fmoe_swiglu_bwd_ragged(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
                            const int64_t* rows_used, void* stream);
+
+/* Derivative of the FMOE_ACT_GELU epilogue: from the pre-activations h ([rows, n] bf16,
+ * recomputed with FMOE_ACT_NONE) and the gradient of gelu(h), writes grad_h = grad_act *
+ * gelu'(h) ([rows, n] bf16), the operand of the first GEMM's data and weight gradients
+ * (the backward of nn.GELU() between the two linears of tiny_model.py:70-74). n % 8 == 0. */
+int fmoe_gelu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t n,
+                  void* stream);
 
 /* ---- host-buffer call -------------------------------------------------------- */
 /*

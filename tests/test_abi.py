@@ -27,7 +27,7 @@ def test_every_declared_symbol_is_exported():
     handle = _lib.lib()
     for name in declared_functions():
         assert hasattr(handle, name), f"{name} is declared but not exported"
-    assert handle.fmoe_abi_version() == 1
+    assert handle.fmoe_abi_version() == 2
     assert handle.fmoe_status_name(-3) == b"FMOE_ERR_WORKSPACE"
 
 

@@ -111,14 +111,17 @@ def test_regroup_indices_small():
     assert empty[0].numel() == 0 and empty[2] == [0, 0]
 
 
-@pytest.mark.parametrize("world,E,K", [(2, 8, 2), (4, 8, 3), (4, 16, 4)])
-def test_fused_layout_routes_every_row_there_and_back(world, E, K):
+@pytest.mark.parametrize("world,E,K,cap_share", [(2, 8, 2, 1.0), (4, 8, 3, 1.0), (4, 16, 4, 1.0),
+                                                 (2, 8, 2, 0.4), (4, 16, 4, 0.2)])  # fmt: skip
+def test_fused_layout_routes_every_row_there_and_back(world, E, K, cap_share):
     """The placement arithmetic of the peer-store exchange, emulated with plain tensors: every
     rank's rows reach the right expert's owner in expert-major order, and the return addresses
-    bring each result back to the slot it came from."""
+    bring each result back to the slot it came from. With a receive buffer smaller than the
+    rows routed to a rank (cap_share < 1) the copies that do not fit are dropped by their
+    senders, the experts see only rows that arrived, and a dropped copy's result is zero."""
     T, D = 40, 3
     el = E // world
-    cap = world * T * K
+    cap = int(world * T * K * cap_share)
     torch.manual_seed(world * 100 + E)
     ranks = []
     for r in range(world):
@@ -132,25 +135,34 @@ def test_fused_layout_routes_every_row_there_and_back(world, E, K):
     C = torch.stack([r["counts"] for r in ranks])
     recv = [torch.full((cap, D), float("nan")) for _ in range(world)]
     ret = [torch.full((T * K, D), float("nan")) for _ in range(world)]
+    kept = [torch.ones(T * K, dtype=torch.bool) for _ in range(world)]
     layouts = [exchange.fused_layout(C, r, cap, D) for r in range(world)]  # row_bytes = D "bytes" per row
     for r, rk in enumerate(ranks):  # dispatch: what the permute kernel computes per routed copy
         dst_row0 = layouts[r][0]
         for t in range(T):
             for k in range(K):
                 e = int(rk["idx"][t, k])
-                row = int(dst_row0[e]) + int(rk["slot_of"][t * K + k]) - int(rk["offsets"][e])
+                slot = int(rk["slot_of"][t * K + k])
+                row = int(dst_row0[e]) + slot - int(rk["offsets"][e])
+                if row >= cap:  # no room: dropped, and the owner's return row is cleared
+                    ret[r][slot] = 0.0
+                    kept[r][slot] = False
+                    continue
                 assert torch.isnan(recv[e // el][row]).all()  # nobody else writes this row
                 recv[e // el][row] = rk["x"][t]
     for d in range(world):  # experts: scale by (global expert id + 1), then the return stores
-        _, counts_local, offsets_local, src_rank, origin_byte = layouts[d]
-        assert int(counts_local.sum()) == int(C[:, d * el : (d + 1) * el].sum())
+        _, counts_local, offsets_local, src_rank, origin_byte, used = layouts[d]
+        routed_here = int(C[:, d * el : (d + 1) * el].sum())
+        assert int(counts_local.sum()) == min(routed_here, cap) == int(used)
+        assert bool(((offsets_local + counts_local) <= cap).all())
         for e in range(el):
             for i in range(int(offsets_local[e]), int(offsets_local[e] + counts_local[e])):
                 assert not torch.isnan(recv[d][i]).any()
                 ret[int(src_rank[i])][int(origin_byte[i]) // D] = recv[d][i] * (d * el + e + 1)
+    assert cap_share >= 1.0 or not all(bool(k.all()) for k in kept)  # the small buffers did overflow
     for r, rk in enumerate(ranks):
         expert_of_slot = torch.repeat_interleave(torch.arange(E), rk["counts"])
-        want = rk["x"][rk["rev"]] * (expert_of_slot + 1).float()[:, None]
+        want = rk["x"][rk["rev"]] * (expert_of_slot + 1).float()[:, None] * kept[r][:, None]
         assert torch.equal(ret[r], want)
 
 
@@ -221,3 +233,41 @@ def test_static_exchange_single_rank_is_identity():
     out = moe.compute_experts_static(rows)  # shares of 3, 3, 1 rows
     want = torch.cat([moe.experts[0](rows[:3]), moe.experts[1](rows[3:6]), moe.experts[2](rows[6:])])
     assert torch.equal(out, want)
+
+
+def _bad_split_worker(rank, world, port, fail_q):
+    """A rank whose send counts do not match its rows learns so on the host, before any
+    collective is enqueued: no rank is left waiting inside a mismatched all-to-all."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        rows = torch.randn(6, 3)
+        for out_splits, in_splits in (([3, 3], [3, 4]), ([3, 3], [3]), ([3, -1], [3, 3])):
+            with pytest.raises(ValueError):
+                exchange.all_to_all_rows(rows, out_splits, in_splits)
+        got = exchange.all_to_all_rows(rows, [3, 3], [3, 3])  # the group is still usable afterwards
+        assert got.shape == (6, 3)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:
+        import traceback
+
+        fail_q.put(f"rank {rank}: {exc}\n{traceback.format_exc()}")
+        raise
+
+
+def test_mismatched_splits_raise_before_the_collective():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_bad_split_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    msgs = []
+    while not q.empty():
+        msgs.append(q.get())
+    assert not msgs, "\n".join(msgs)
+    assert all(p.exitcode == 0 for p in procs)

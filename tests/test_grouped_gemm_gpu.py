@@ -12,13 +12,15 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _reference(a, w, counts, swiglu):
+def _reference(a, w, counts, swiglu, gelu=False):
     out, o = [], 0
     for e, n in enumerate(counts):
         h = a[o : o + n].float() @ w[e].float().t()
         if swiglu:
             ff = h.shape[1] // 2
             h = torch.nn.functional.silu(h[:, :ff]) * h[:, ff:]
+        if gelu:
+            h = torch.nn.functional.gelu(h)  # the exact (erf) form, nn.GELU()'s default
         out.append(h)
         o += n
     return torch.cat(out, 0)
@@ -62,8 +64,8 @@ def test_grouped_gemm_matches_fp32_reference(counts, K, N, swiglu):
 
 
 def test_rows_outside_every_expert_stay_zero_and_backward_runs():
-    a, w, off, cnt = _case([100, 60], 128, 256, False, seed=3)
-    pad = torch.randn(40, 128, device=DEV).bfloat16()
+    a, w, off, cnt = _case([100, 60], 256, 256, False, seed=3)
+    pad = torch.randn(40, 256, device=DEV).bfloat16()
     a2 = torch.cat([a[:100], pad, a[100:]], 0).requires_grad_(True)  # 40 unowned rows in the middle
     off2 = torch.tensor([0, 140], dtype=torch.int64, device=DEV)
     w2 = w.clone().requires_grad_(True)
@@ -96,6 +98,70 @@ def test_unsupported_shapes_raise():
         experts.grouped_gemm(a, w[:, :100].contiguous(), off, cnt)  # N % 256
     with pytest.raises(ValueError):
         experts.grouped_gemm(a.float(), w.float(), off, cnt)
+    # a width only the forward tiles: asking for gradients raises too, up front (no library fallback)
+    experts.grouped_gemm(a, w, off, cnt)
+    with pytest.raises(ValueError, match="gradients"):
+        experts.grouped_gemm(a.clone().requires_grad_(True), w, off, cnt)  # K = 64 is not a multiple of 256
+
+
+@pytest.mark.parametrize("counts,K,N", [([128], 64, 256), ([200, 0, 5, 300], 512, 512), ([513, 127, 129], 256, 1024)])
+def test_gelu_epilogue_matches_fp32_reference(counts, K, N):
+    """The reference's own expert is Linear-GELU-Linear: the first product with the exact GELU
+    fused into the epilogue."""
+    a, w, off, cnt = _case(counts, K, N, False, seed=31)
+    c = experts.grouped_gemm(a, w, off, cnt, activation=experts.ACT_GELU)
+    torch.cuda.synchronize()
+    assert ops.read_status() == 0
+    ref = _reference(a, w, counts, False, gelu=True)
+    err = float((c.float() - ref).abs().max() / ref.abs().max())
+    assert err <= 1e-2, err
+
+
+def test_gelu_ffn_forward_and_backward_match_fp32_autograd():
+    counts, D, FF = [300, 17, 0, 200], 256, 512
+    a, w1, off, cnt = _case(counts, D, FF, False, seed=33)
+    gen = torch.Generator(device=DEV).manual_seed(34)
+    w2 = (torch.randn(len(counts), D, FF, generator=gen, device=DEV) / FF**0.5).bfloat16()
+    g = torch.randn(sum(counts), D, generator=gen, device=DEV).bfloat16()
+    a.requires_grad_(True), w1.requires_grad_(True), w2.requires_grad_(True)
+    y = experts.grouped_gelu_ffn(a, w1, w2, off, cnt, covers_all_rows=True)
+    y.backward(g)
+    torch.cuda.synchronize()
+    assert ops.read_status() == 0
+    a32, w1_32, w2_32 = (t.detach().float().requires_grad_(True) for t in (a, w1, w2))
+    hidden = _reference(a32, w1_32, counts, False, gelu=True)
+    ref = _reference(hidden, w2_32, counts, False)
+    ref.backward(g.float())
+    tol = REL_TOL[torch.bfloat16]
+    assert float((y.float() - ref).abs().max() / ref.abs().max()) <= tol
+    for got, want, what in ((a.grad, a32.grad, "dx"), (w1.grad, w1_32.grad, "dw1"), (w2.grad, w2_32.grad, "dw2")):
+        err = float((got.float() - want).abs().max() / want.abs().max())
+        assert err <= tol, (what, err)
+
+
+def test_counts_that_run_past_the_rows_are_cut_off():
+    """Counts that claim more rows than A has (what an overflowing receive buffer would hand
+    over): the last expert is cut at A's end, nothing beyond A or C is read or written, and
+    the status word says so."""
+    real = [200, 100]
+    a, w, off, _ = _case(real, 256, 256, False, seed=41)
+    claimed = torch.tensor([200, 260], dtype=torch.int64, device=DEV)  # 160 rows more than exist
+    guard = torch.full((64, 256), 7.0, dtype=torch.bfloat16, device=DEV)
+    c = torch.cat([torch.zeros(300, 256, dtype=torch.bfloat16, device=DEV), guard], 0)  # C with a canary behind it
+    experts._launch(a, w, off, claimed, experts.ACT_NONE, out=c[:300])
+    torch.cuda.synchronize()
+    assert ops.read_status() & 2
+    assert bool((c[300:] == 7.0).all()), "rows behind C were written"
+    ref = _reference(a, w, real, False)
+    assert float((c[:300].float() - ref).abs().max() / ref.abs().max()) <= 1e-2
+    # the same through a table of row addresses that has exactly one entry per row of A
+    out = torch.zeros(300 + 64, 256, dtype=torch.bfloat16, device=DEV)
+    ptrs = out.data_ptr() + torch.arange(300, device=DEV, dtype=torch.int64) * 512
+    experts._launch(a, w, off, claimed, experts.ACT_NONE, row_ptrs=ptrs)
+    torch.cuda.synchronize()
+    assert ops.read_status() & 2
+    assert float(out[300:].abs().max()) == 0.0
+    assert float((out[:300].float() - ref).abs().max() / ref.abs().max()) <= 1e-2
 
 
 def test_row_map_scatters_the_output_rows():
@@ -193,3 +259,58 @@ def test_swiglu_derivative_over_a_capacity_sized_buffer():
         err = float((out[:n].float() - want[:n]).abs().max() / want.abs().max())
         assert err <= REL_TOL[torch.bfloat16], err
         assert bool((out[n:] == sentinel).all()), "rows past the count were written"
+
+
+def test_weight_gradient_ignores_nan_rows_behind_the_last_expert():
+    """Capacity-sized operands: rows behind the last expert's end hold whatever the allocator
+    left there, NaN bit patterns included. The ragged last chunk is cleared in BOTH operands
+    before the MMAs, so none of it reaches the weight gradient (0 x NaN would be NaN)."""
+    counts = [130, 70]  # 200 rows in use; the last 64-row chunk of expert 1 reaches rows 200..255
+    a, w, off, cnt = _case(counts, 256, 256, False, seed=51)
+    gen = torch.Generator(device=DEV).manual_seed(52)
+    g = torch.randn(200, 256, generator=gen, device=DEV).bfloat16()
+    nan_tail = torch.full((120, 256), float("nan"), dtype=torch.bfloat16, device=DEV)
+    inf_tail = torch.full((120, 256), float("inf"), dtype=torch.bfloat16, device=DEV)
+    for a_tail, g_tail in ((nan_tail, nan_tail), (inf_tail, torch.zeros_like(nan_tail)), (nan_tail, inf_tail)):
+        a_cap, g_cap = torch.cat([a, a_tail], 0), torch.cat([g, g_tail], 0)
+        grad_w = experts._wgrad(g_cap, a_cap, w.shape, off, cnt)
+        torch.cuda.synchronize()
+        assert ops.read_status() == 0
+        assert bool(torch.isfinite(grad_w.float()).all())
+        for e, (o, n) in enumerate(zip([0, 130], counts)):
+            ref = g[o : o + n].float().t() @ a[o : o + n].float()
+            assert float((grad_w[e].float() - ref).abs().max() / ref.abs().max()) <= REL_TOL[torch.bfloat16]
+
+
+def test_expert_parallel_layer_sized_products():
+    """The sizes the expert-parallel layer runs: one rank of eight (32 experts x 2048 rows,
+    7168 -> 2 x 2048 SwiGLU and 2048 -> 7168) and a single rank (256 experts x 256 rows, where
+    the weight tensor map has 1,048,576 rows). Checked on whole experts at the front, the
+    middle and the end against fp32 products of the same bf16 values."""
+    D, FF = 7168, 2048
+    for E, per in ((32, 2048), (256, 256)):
+        R = E * per
+        gen = torch.Generator(device=DEV).manual_seed(60 + E)
+        cnt = torch.full((E,), per, dtype=torch.int64, device=DEV)
+        jitter = torch.randint(-(per // 8), per // 8 + 1, (E // 2,), generator=gen, device=DEV)
+        cnt[: E // 2] += jitter
+        cnt[E // 2 :] -= jitter.flip(0)
+        off = torch.cumsum(cnt, 0) - cnt
+        x = torch.randn(R, D, generator=gen, device=DEV, dtype=torch.bfloat16)
+        wgu = torch.empty(E, 2 * FF, D, device=DEV, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        wd = torch.empty(E, D, FF, device=DEV, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        with torch.no_grad():
+            hidden = experts.grouped_gemm(x, wgu, off, cnt, swiglu=True, covers_all_rows=True)
+            y = experts.grouped_gemm(hidden, wd, off, cnt, covers_all_rows=True)
+        torch.cuda.synchronize()
+        assert ops.read_status() == 0
+        for e in (0, E // 2 - 1, E // 2, E - 1):
+            o, n = int(off[e]), int(cnt[e])
+            h = x[o : o + n].float() @ wgu[e].float().t()
+            ref_h = torch.nn.functional.silu(h[:, :FF]) * h[:, FF:]
+            err_h = float((hidden[o : o + n].float() - ref_h).abs().max() / ref_h.abs().max())
+            ref_y = hidden[o : o + n].float() @ wd[e].float().t()
+            err_y = float((y[o : o + n].float() - ref_y).abs().max() / ref_y.abs().max())
+            assert err_h <= 1e-2 and err_y <= 1e-2, (E, e, err_h, err_y)
+        del x, wgu, wd, hidden, y
+        torch.cuda.empty_cache()

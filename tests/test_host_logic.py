@@ -70,12 +70,34 @@ def test_expert_and_exchange_wrappers_refuse_cpu_and_bad_shapes():
         ep_fused.FusedExpertParallel(object(), 16)
     # the layout arithmetic of the fused exchange is plain tensor code and runs anywhere
     C = torch.tensor([[3, 0, 2, 1], [1, 4, 0, 2]])
-    dst_row0, counts_local, offsets_local, src_rank, origin_byte = exchange.fused_layout(C, rank=1, cap_rows=16, row_bytes=8)
+    dst_row0, counts_local, offsets_local, src_rank, origin_byte, used = exchange.fused_layout(
+        C, rank=1, cap_rows=16, row_bytes=8)  # fmt: skip
     assert counts_local.tolist() == [2, 3] and offsets_local.tolist() == [0, 2]  # rank 1 owns experts 2 and 3
+    assert used.tolist() == [5]
     # on the owner, experts follow each other and rank 0's rows of an expert precede mine
     assert dst_row0.tolist() == [3, 4, 2, 3]
     assert src_rank[:5].tolist() == [0, 0, 0, 1, 1]
     assert origin_byte[:5].tolist() == [3 * 8, 4 * 8, 5 * 8, 5 * 8, 6 * 8]
+
+
+@pytest.mark.parametrize("cap", [0, 1, 3, 4, 5, 9])
+def test_fused_layout_stops_at_the_receive_capacity(cap):
+    """More rows routed to a rank than its receive buffer holds: the counts handed to the
+    experts stop at the capacity (offsets + counts never pass it), the senders' placement is
+    unchanged (they drop what lands beyond it), and the rows in use are the capacity."""
+    from fastmoe_b200 import exchange
+
+    C = torch.tensor([[3, 0, 2, 1], [1, 4, 0, 2]])  # rank 0 receives 3+1+0+4 = 8 rows, rank 1 receives 5
+    for rank, received in ((0, [4, 4]), (1, [2, 3])):
+        dst_row0, counts, offsets, _, _, used = exchange.fused_layout(C, rank, cap, 8)
+        full = exchange.fused_layout(C, rank, 64, 8)
+        assert dst_row0.tolist() == full[0].tolist()
+        assert bool(((offsets + counts) <= cap).all()) and bool((counts >= 0).all())
+        assert int(used) == min(sum(received), cap) == int(counts.sum())
+        first = 0
+        for e, n in enumerate(received):  # what fits of each expert, in expert order
+            assert int(counts[e]) == max(0, min(n, cap - first))
+            first += n
 
 
 def test_swiglu_expert_container_behaves_like_a_module_list():
