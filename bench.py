@@ -4,7 +4,7 @@
 
 One step = one full combine of one synthetic batch through the public operator
 `grouped_weighted_scatter_add(expert_tensors, indices, weights, out_shape)`:
-plan build (inverse map, 4 small kernels) + token-major gather kernel, output
+plan build (inverse map, one cooperative launch) + token-major gather kernel, output
 freshly produced. The default workload is the combine microbenchmark
 (T=8192 tokens, D=16384, E=256 experts, top-8, bf16; 256 disjoint expert output
 matrices, 2.15 GB of rows, which exceeds the 126 MB L2, so every step streams
@@ -16,16 +16,23 @@ Rank 0 prints ONE JSON line. Keys beyond the usual ones:
             (pinned host inputs -> device -> combine -> host), copies timed
   roofline  the gather kernel alone: algorithmic bytes / its CUDA-event time,
             against the measured HBM copy bandwidth of this GPU pool
-  cpu_baseline  the CPU restatement of the reference's path (oracle/), all host
-            threads, timed in this run on the same workload
+  cpu_baseline  the reference's own CPU path (the unmodified package, when
+            oracle/install_ref.py has installed it; else its C port in oracle/),
+            timed in this run on a stated sample of the same workload
+  also      the other single-GPU configurations, a few steps each, outside the
+            headline timing: the skewed (Zipf) combine and the dispatch + combine
+            chain under autograd, each with its own roofline entry
+  ep_layer  the expert-parallel MoE layer at this world size, with a parity record
+            (sampled tokens against an fp32 evaluation over all experts, forward
+            and token gradients, and the device status word)
 
 With --gpus N > 1 (under torchrun) every rank runs an independent replica of the
-workload: the combine has no cross-GPU step ("replicas only"); the aggregate is
-the sum over ranks divided by the slowest rank's time.
+combine workload: the combine has no cross-GPU step ("replicas only"); the aggregate
+is the sum over ranks divided by the slowest rank's time. The expert-parallel layer
+in `ep_layer` is the part that shards (experts over ranks, tokens exchanged).
 
-`--impl reference` times the reference's CPU implementation of the path (the
-oracle port; the reference is pure Python over torch and has nothing to compile)
-on the box's host cores, same workload, same metric.
+`--impl reference` times the reference's CPU implementation of the path on the box's
+host cores, same workload, same metric, inputs built on the host.
 """
 
 from __future__ import annotations
@@ -72,8 +79,8 @@ GEMM = {
     "grouped_swiglu_ffn_ncu_E32_R8192_D7168_ff2048": (32, 8192, 7168, 2048),  # 256 rows per expert, for ncu
 }
 
-# DRAM bytes (read + write) of one gather launch on the default workload: the ncu
-# capture of the quarter-size case (profiles/combine_gather_cfg2.md) scaled by its
+# DRAM bytes (read + write) of one gather launch on the default workload: an ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum) of the quarter-size case, scaled by its
 # 4x tokens; traffic grows in proportion to tokens.
 NCU_TRAFFIC_BYTES = {DEFAULT_WORKLOAD: 4 * (537_092_352 + 45_110_528)}
 
@@ -164,16 +171,23 @@ def host_copy(wl):
     """Pinned host copies of the workload (bf16 rows as uint16 bit patterns for numpy)."""
     import torch
 
-    experts = [torch.empty(e.shape, dtype=e.dtype).pin_memory() for e in wl.experts]
+    pin = torch.cuda.is_available()
+    experts = [torch.empty(e.shape, dtype=e.dtype, pin_memory=pin) for e in wl.experts]
     for h, d in zip(experts, wl.experts):
         h.copy_(d)
-    idx = wl.indices.cpu().pin_memory()
-    w = wl.weights.cpu().pin_memory()
-    torch.cuda.synchronize()
+    idx = wl.indices.cpu()
+    w = wl.weights.cpu()
+    if pin:
+        idx, w = idx.pin_memory(), w.pin_memory()
+        torch.cuda.synchronize()
     return experts, idx, w
 
 
-def cpu_pass(host, T, D):
+def host_threads():
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def cpu_pass_port(host, T, D):
     """One combine on the host cores with the reference's CPU arithmetic for the tensors' dtype
     (oracle port: bf16 product and per-call fp32 accumulation for bf16, plain fp32 otherwise)."""
     import numpy as np
@@ -194,37 +208,81 @@ def cpu_pass(host, T, D):
     return time.perf_counter() - t0
 
 
+class CpuArm:
+    """The reference's CPU path on this box's host cores, on a bounded sample of a combine
+    workload: the rows of the first `experts` expert matrices (all T output rows), sized so
+    that one pass takes about a second. kind "reference" runs the unmodified package's
+    `grouped_weighted_scatter_add` on CPU tensors (src/fastmoe/kernels/ops.py:373-384, torch's
+    own thread pool); kind "port" runs the C/OpenMP restatement of it when the package is not
+    installed on this machine."""
+
+    def __init__(self, host, T, D, force_port=False):
+        import torch
+
+        import oracle
+
+        self.host, self.T, self.D = host, T, D
+        self.ref = None if force_port else oracle.reference_ops()
+        experts, idx, w = host
+        E = len(experts)
+        # the reference's torch path manages 1-2 GB/s, the port ~10x that: a quarter of the experts
+        # keeps one reference pass near a second; the port takes the whole workload
+        self.n_experts = E if self.ref is None else max(1, E // 4)
+        self.rows = sum(int(e.shape[0]) for e in experts[: self.n_experts])
+        es = experts[0].element_size()
+        self.bytes = (self.rows * D * es + T * D * es + self.rows * (idx.element_size() + w.element_size())
+                      + self.n_experts * 20)  # fmt: skip
+        self.kind = "port" if self.ref is None else "reference"
+        if self.ref is not None:
+            torch.set_num_threads(host_threads())
+            self.cores = torch.get_num_threads()
+        else:
+            self.cores = oracle.use_all_cores()
+
+    def one_pass(self):
+        experts, idx, w = self.host
+        sub = (experts[: self.n_experts], idx[: self.rows], w[: self.rows])
+        if self.ref is None:
+            return cpu_pass_port(sub, self.T, self.D)
+        t0 = time.perf_counter()
+        self.ref.grouped_weighted_scatter_add(sub[0], sub[1], sub[2], (self.T, self.D))
+        return time.perf_counter() - t0
+
+    def describe(self):
+        what = ("the unmodified reference package's CPU path (torch index_add_ per expert)" if self.ref is not None
+                else "C/OpenMP port of the reference's CPU path")  # fmt: skip
+        return (f"{what} on the rows of the first {self.n_experts} of {len(self.host[0])} expert matrices "
+                f"({self.rows} rows into all {self.T} output rows); GB/s counts that sample's algorithmic bytes")  # fmt: skip
+
+
 # The reference publishes one number for this path: 2.61 ms for its grouped kernel on an H100
 # at its own preset (README.md:88). In this bench's unit that is the preset's algorithmic
 # bytes over 2.61 ms.
 PUBLISHED_MS = {"combine_reference_preset_fp32_T4096_D16384_E256_top4": 2.61}
 
 
+def workload_config(name):
+    T, D, E, K, routing = WORKLOADS[name]
+    return {"workload": name, "T": T, "D": D, "E": E, "top_k": K, "routing": routing}
+
+
 def run_reference(args, rank):
-    """The reference arm: the CPU path (oracle port) on this box's host cores."""
+    """The reference arm: the reference's CPU path on this box's host cores, inputs built on the host."""
     if rank != 0:
         return
     import torch
 
-    import oracle
     from fastmoe_b200.workloads import make_combine_workload
 
     T, D, E, K, routing = WORKLOADS[args.workload]
-    device = "cuda" if torch.cuda.is_available() else "cpu"
     dtype = torch.float32 if "_fp32_" in args.workload else torch.bfloat16
-    wl = make_combine_workload(T, D, E, K, dtype, routing, seed=0, device=device)
-    if device == "cuda":
-        host = host_copy(wl)
-    else:
-        host = (wl.experts, wl.indices, wl.weights)
-    nbytes = wl.algorithmic_bytes()
-    del wl
+    wl = make_combine_workload(T, D, E, K, dtype, routing, seed=0, device="cpu")
+    arm = CpuArm((wl.experts, wl.indices, wl.weights), T, D, force_port=args.cpu_port)
     for _ in range(args.warmup):
-        cpu_pass(host, T, D)
-    t = [cpu_pass(host, T, D) for _ in range(args.steps)]
+        arm.one_pass()
+    t = [arm.one_pass() for _ in range(args.steps)]
     total = sum(t)
-    value = nbytes * args.steps / total / 1e9
-    cores = oracle.num_threads()
+    value = arm.bytes * args.steps / total / 1e9
     line = {
         "impl": "reference",
         "metric": METRIC,
@@ -239,31 +297,47 @@ def run_reference(args, rank):
         "vs_baseline": None,
         "dtype": "f32" if dtype == torch.float32 else "bf16",
         "data": "synthetic",
-        "config": {"workload": args.workload, "T": T, "D": D, "E": E, "top_k": K, "routing": routing},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": "the full workload, every step one complete combine on the host"},
+        "config": workload_config(args.workload),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": arm.cores, "kind": arm.kind, "sample": arm.describe()},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }  # fmt: skip
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args, rank, world, local_rank):
+def bind_to_gpu_cores(index):
+    """Restricts this process to the host cores NVML reports as local to GPU `index`, so that the
+    pinned staging buffers allocated afterwards come from that GPU's memory node. Returns the
+    number of cores, or None when NVML or the affinity call is not available."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cores = {64 * i + b for i, word in enumerate(mask) for b in range(64) if (word >> b) & 1}
+        cores &= os.sched_getaffinity(0)
+        if cores:
+            os.sched_setaffinity(0, cores)
+            return len(cores)
+    except Exception:
+        pass
+    return None
+
+
+def combine_record(name, rank, world, device, steps, warmup, keep=False):
+    """Times `steps` combines of workload `name` through the public operator. Returns a dict
+    (elapsed_ms over the steps, per-launch kernel and plan times, host enqueue time, ...) and,
+    with keep=True, the workload and the last output for the callers that go on with them."""
     import torch
     import torch.distributed as dist
 
-    from fastmoe_b200 import _lib
     from fastmoe_b200.kernels import ops
     from fastmoe_b200.workloads import make_combine_workload
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the product has no CPU path")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    _lib.lib()  # fail now if the CUDA library is missing
-
-    T, D, E, K, routing = WORKLOADS[args.workload]
-    dtype = torch.float32 if "_fp32_" in args.workload else torch.bfloat16
+    T, D, E, K, routing = WORKLOADS[name]
+    dtype = torch.float32 if "_fp32_" in name else torch.bfloat16
     wl = make_combine_workload(T, D, E, K, dtype, routing, seed=rank, device=device)
     nbytes = wl.algorithmic_bytes()
     shape = (T, D)
@@ -276,18 +350,19 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         out = step()
     barrier()
-
     ops.kernel_events = {}  # entry point -> (start, end) CUDA events around every call
     launches0 = ops.launch_count
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(device.index) as clocks:
         barrier()
         start.record()
-        for _ in range(args.steps):
+        t0 = time.perf_counter()
+        for _ in range(steps):
             out = step()
+        host_s = time.perf_counter() - t0  # time to ENQUEUE the steps: the host's share
         end.record()
         barrier()
     elapsed_ms = start.elapsed_time(end)
@@ -296,8 +371,57 @@ def run_ours(args, rank, world, local_rank):
     launches = ops.launch_count - launches0
     ops.kernel_events = None
     assert ops.read_status(device) == 0, "kernels flagged skipped rows"
-    checksum = float(out.float().abs().mean())
-    assert checksum > 0.0
+    assert float(out.float().abs().mean()) > 0.0
+    rec = {
+        "elapsed_ms": elapsed_ms, "bytes": nbytes, "launches": launches, "clocks": clocks.summary(),
+        "kernel_ms": statistics.mean(gather_ms) if gather_ms else None,
+        "plan_ms": statistics.mean(plan_ms) if plan_ms else None,
+        "host_enqueue_ms_per_step": host_s / steps * 1e3, "rows": wl.N, "max_rows_per_expert": max(wl.counts),
+    }  # fmt: skip
+    return (rec, wl, out) if keep else (rec, None, None)
+
+
+def roofline_of(rec, name):
+    peak, peak_kind = measured_peak()
+    achieved = rec["bytes"] / (rec["kernel_ms"] / 1e3) / 1e9 if rec["kernel_ms"] else None
+    return {
+        "bound": "hbm",
+        "kernel": "gather_sum_kernel (combine forward)",
+        "achieved": achieved,
+        "peak": peak,
+        "peak_kind": peak_kind,
+        "unit": "GB/s",
+        "frac": achieved / peak if achieved else None,
+        "frac_of_8TBs_spec": achieved / 8000.0 if achieved else None,
+        "kernel_ms": rec["kernel_ms"],
+        "algorithmic_bytes": rec["bytes"],
+        "traffic": NCU_TRAFFIC_BYTES.get(name),
+        "plan_build_ms": rec["plan_ms"],
+    }
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    from fastmoe_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    _lib.lib()  # fail now if the CUDA library is missing
+    local_cores = bind_to_gpu_cores(local_rank) if world > 1 else None
+
+    T, D, E, K, routing = WORKLOADS[args.workload]
+    dtype = torch.float32 if "_fp32_" in args.workload else torch.bfloat16
+    rec, wl, out = combine_record(args.workload, rank, world, device, args.steps, args.warmup, keep=True)
+    nbytes, elapsed_ms = rec["bytes"], rec["elapsed_ms"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     # ---- end to end through the C ABI with host buffers ----------------------------
     host = host_copy(wl)
@@ -338,51 +462,52 @@ def run_ours(args, rank, world, local_rank):
     elapsed_ms, e2e_s = stats.tolist()
     value = nbytes * world * args.steps / (elapsed_ms / 1e3) / 1e9
     e2e_value = nbytes * world * e2e_steps / e2e_s / 1e9
+    n_rows = wl.N
+    del wl, out, arena, out_host
+    torch.cuda.empty_cache()
+
+    # CPU baseline on rank 0 at N=1 only: a few passes of the bounded sample
+    cpu_baseline = None
+    if rank == 0 and world == 1:
+        arm = CpuArm(host, T, D, force_port=args.cpu_port)
+        arm.one_pass()
+        cpu_t = [arm.one_pass() for _ in range(3)]
+        cpu_baseline = {
+            "value": arm.bytes / statistics.median(cpu_t) / 1e9, "unit": UNIT, "cores": arm.cores, "kind": arm.kind,
+            "sample": arm.describe() + "; median of 3 passes after 1 warm-up", "ms": statistics.median(cpu_t) * 1e3,
+        }  # fmt: skip
+        if arm.kind == "reference":  # the C port of the same path beside it, on the whole workload
+            import oracle
+
+            cpu_pass_port(host, T, D)
+            port_s = statistics.median(cpu_pass_port(host, T, D) for _ in range(3))
+            cpu_baseline["port"] = {"value": nbytes / port_s / 1e9, "unit": UNIT, "cores": oracle.num_threads(),
+                                    "ms": port_s * 1e3, "sample": "C/OpenMP port, the full workload"}  # fmt: skip
+    del host, hex_, hidx, hw
+
+    # ---- the other single-GPU configurations, outside the headline timing -------------
+    also = None
+    if args.workload == DEFAULT_WORKLOAD and world == 1 and not args.no_also:
+        sub_steps = max(3, min(args.steps, 10))
+        r3, _, _ = combine_record("combine_cfg3_zipf_bf16_T8192_D16384_E256_top8", rank, world, device, sub_steps, 3)
+        also = {"combine_cfg3": {
+            "config": workload_config("combine_cfg3_zipf_bf16_T8192_D16384_E256_top8"),
+            "value": r3["bytes"] * sub_steps / (r3["elapsed_ms"] / 1e3) / 1e9, "unit": UNIT,
+            "ms_per_step": r3["elapsed_ms"] / sub_steps, "steps": sub_steps, "max_rows_per_expert": r3["max_rows_per_expert"],
+            "roofline": roofline_of(r3, "combine_cfg3_zipf_bf16_T8192_D16384_E256_top8"),
+        }}  # fmt: skip
+        torch.cuda.empty_cache()
+        also["dispatch_combine_cfg4"] = cfg4_record("dispatch_combine_cfg4_bf16_T16384_D7168_E256_top8", rank, world,
+                                                    local_rank, sub_steps, 3, cpu=False)  # fmt: skip
+        torch.cuda.empty_cache()
 
     # second part of the headline metric: the expert-parallel MoE layer at this world size
     ep = None
     if args.workload == DEFAULT_WORKLOAD and not args.no_ep:
-        n_rows = wl.N
-        del wl, out, arena
-        torch.cuda.empty_cache()
         ep = ep_layer_bench(rank, world, local_rank, min(args.steps, 20), min(args.warmup, 5), None, args.ep_mode)
-    else:
-        n_rows = wl.N
 
     if rank != 0:
         return
-
-    peak, peak_kind = measured_peak()
-    kernel_ms = statistics.mean(gather_ms) if gather_ms else None
-    achieved = nbytes / (kernel_ms / 1e3) / 1e9 if kernel_ms else None
-    roofline = {
-        "bound": "hbm",
-        "kernel": "gather_sum_kernel (combine forward)",
-        "achieved": achieved,
-        "peak": peak,
-        "peak_kind": peak_kind,
-        "unit": "GB/s",
-        "frac": achieved / peak if achieved else None,
-        "frac_of_8TBs_spec": achieved / 8000.0 if achieved else None,
-        "kernel_ms": kernel_ms,
-        "algorithmic_bytes": nbytes,
-        "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-        "plan_build_ms": statistics.mean(plan_ms) if plan_ms else None,
-    }
-
-    # CPU baseline: the oracle port on this box's cores, whole workload, a few passes
-    import oracle
-
-    cpu_pass(host, T, D)
-    cpu_t = [cpu_pass(host, T, D) for _ in range(3)]
-    cpu_baseline = {
-        "value": nbytes / statistics.median(cpu_t) / 1e9,
-        "unit": UNIT,
-        "cores": oracle.num_threads(),
-        "kind": "port",
-        "sample": "the full workload, median of 3 complete combines after 1 warm-up",
-        "ms": statistics.median(cpu_t) * 1e3,
-    }
 
     line = {
         "metric": METRIC,
@@ -398,17 +523,21 @@ def run_ours(args, rank, world, local_rank):
                         if args.workload in PUBLISHED_MS and world == 1 else None),
         "dtype": "f32" if dtype == torch.float32 else "bf16",
         "data": "synthetic",
-        "config": {
-            "workload": args.workload, "T": T, "D": D, "E": E, "top_k": K, "routing": routing,
+        "config": workload_config(args.workload),
+        "notes": {
             "rows": n_rows, "l2": "inputs (%.2f GB) exceed the 126 MB L2; no flush needed" % (nbytes / 1e9),
-            "multi_gpu": "replicas only",
+            "multi_gpu": "replicas only (the combine has no cross-GPU step; ep_layer is the sharded part)",
+            "host_enqueue_ms_per_step": rec["host_enqueue_ms_per_step"],
+            "pinned_buffers": (f"allocated after binding the rank to its GPU's {local_cores} local cores"
+                               if local_cores else "allocated with the process's default affinity"),
         },
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "call": "fmoe_combine_host (C ABI, pinned host buffers)"},
-        "gpu_launches": launches,
-        "roofline": roofline,
+        "gpu_launches": rec["launches"],
+        "roofline": roofline_of(rec, args.workload),
         "cpu_baseline": cpu_baseline,
-        "clocks": clocks.summary(),
+        "clocks": rec["clocks"],
+        "also": also,
         "ep_layer": ep,
     }  # fmt: skip
     print(json.dumps(line), flush=True)
@@ -504,6 +633,7 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, m
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms[0]) / steps
     assert all(bool(torch.isfinite(o.float()).all()) for o in outs)
+    y_fwd = torch.cat([o.reshape(-1, D) for o in outs], 0)  # [T, D], this rank's tokens in order
 
     # the same layer as a training step: forward + backward (tokens, router and expert gradients)
     xt = x.view(1, T, D)
@@ -530,7 +660,10 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, m
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
     train_ms = float(tms[0]) / train_steps
     assert bool(torch.isfinite(gx.float()).all())
-    del gx, gy
+    parity = ep_parity(moe, x, y_fwd, gx.reshape(T, D), gy.reshape(T, D), rank, world, dev, FF)
+    if fused is not None:
+        fused.check_status()
+    del gx, gy, y_fwd
     cpu_baseline = None
     if rank == 0:  # CPU baseline: the expert FFN of a 256-token sample through torch's CPU matmul
         import os
@@ -560,6 +693,11 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, m
         "tokens_per_s": T * world / (ms / 1e3),
         "ms_per_step": ms,
         "tokens_per_rank": T, "micro_batches": MB, "pass": "forward",
+        "expert_groups": fused.expert_groups if fused is not None else 1,
+        "overlap": ("dispatch of expert group g+1 (peer stores, side stream) runs beside the grouped GEMMs of "
+                    "group g; results return from the down-projection's epilogue" if fused is not None
+                    and fused.expert_groups > 1 else "none"),
+        "parity": parity,
         "train_tokens_per_s": T * world / (train_ms / 1e3), "train_ms_per_step": train_ms,
         "train_pass": "forward + backward (tokens, router, expert weights), no optimizer",
         "gemm_tflops_per_gpu": gemm_flops / (ms / 1e3) / 1e12,
@@ -570,6 +708,59 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, m
         "cpu_baseline": cpu_baseline,
         "config": {"D": D, "ff": FF, "E": E, "top_k": K, "experts": "swiglu", "weights": "N(0,0.02) seeded per expert"},
     }  # fmt: skip
+
+
+def ep_parity(moe, x, y, gx, gy, rank, world, dev, FF, sample=128):
+    """Checks what the timed layer computed, on every rank: `sample` of this rank's tokens are
+    evaluated again in fp32 over ALL experts (any rank can regenerate any expert from its
+    global-id seed), forward and token gradient (through the experts and through the router),
+    and compared with the layer's output `y` and the training step's `gx` for upstream gradient
+    `gy`. The ground truth is the single-rank layer over all experts
+    (MoEFeedForward.forward, src/fastmoe/models/tiny_model.py:411-420, with SwiGLU experts).
+    Returns relative errors (largest over ranks) and the device status word; raises if any is
+    out of bounds."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from fastmoe_b200.kernels import ops, routing
+
+    T, D = x.shape
+    K, E, el = moe.top_k, moe.num_experts, moe.num_local_experts
+    status = ops.read_status(dev, reset=False)
+    with torch.no_grad():
+        _, idx_all = routing.route_topk(moe.router(x), K, w_dtype=x.dtype)  # the layer's routing decision
+    pick = torch.randperm(T, generator=torch.Generator(device=dev).manual_seed(4242 + rank), device=dev)[:sample]
+    idx = idx_all[pick]
+    xs = x[pick].float().requires_grad_(True)
+    gate = torch.softmax(torch.gather(xs @ moe.router.weight.detach().float().t(), 1, idx), dim=-1)
+    gen = torch.Generator(device=dev)
+    ref = torch.zeros(sample, D, device=dev)
+    for e in torch.unique(idx).tolist():
+        gen.manual_seed(1000 + e)
+        wgu = torch.empty(2 * FF, D, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        wd = torch.empty(D, FF, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        if rank * el <= e < (rank + 1) * el:  # regenerated weights must be the ones the layer holds
+            assert torch.equal(wgu, moe.experts.w_gate_up[e - rank * el]) and torch.equal(wd, moe.experts.w_down[e - rank * el])
+        rows, ks = (idx == e).nonzero(as_tuple=True)
+        h = xs[rows] @ wgu.float().t()
+        act = (F.silu(h[:, :FF]) * h[:, FF:])
+        act = act + (act.bfloat16().float() - act).detach()  # the layer rounds the activations to bf16 once
+        ref = ref.index_add(0, rows, (act @ wd.float().t()) * gate[rows, ks][:, None])
+        del wgu, wd
+    (ref * gy[pick].float()).sum().backward()
+    fwd_err = float((y[pick].float() - ref.detach()).abs().max() / ref.detach().abs().max())
+    dx_err = float((gx[pick].float() - xs.grad).abs().max() / xs.grad.abs().max())
+    errs = torch.tensor([fwd_err, dx_err, float(status)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+    fwd_err, dx_err, status = float(errs[0]), float(errs[1]), int(errs[2])
+    ops.read_status(dev)  # clear
+    result = {"fwd_rel_err": fwd_err, "dx_rel_err": dx_err, "status": status, "sample": f"{sample} tokens per rank",
+              "bound": 2e-2, "against": "fp32 evaluation over all experts of the same bf16 values"}  # fmt: skip
+    assert status == 0, f"device status word {status} after the expert-parallel steps"
+    assert fwd_err <= 2e-2 and dx_err <= 2e-2, result
+    return result
 
 
 def run_ep(args, rank, world, local_rank):
@@ -682,9 +873,10 @@ def run_gemm(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
-def run_cfg4(args, rank, world, local_rank):
+def cfg4_record(name, rank, world, local_rank, steps, warmup, cpu=True):
     """Index build + dispatch permute + combine, forward and backward, identity experts.
-    Reports whole-chain GB/s of algorithmic bytes and a roofline entry per kernel."""
+    Returns the record of one workload: whole-chain GB/s of algorithmic bytes and a roofline
+    entry per kernel (None on ranks other than 0)."""
     import torch
     import torch.distributed as dist
 
@@ -693,7 +885,7 @@ def run_cfg4(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    T, D, E, K = CFG4[args.workload]
+    T, D, E, K = CFG4[name]
     N, s = T * K, 2
     idx_cpu, w_cpu = routing_uniform(T, E, K, seed=rank)
     idx, gate = idx_cpu.to(dev), w_cpu.to(dev).bfloat16().requires_grad_(True)
@@ -725,7 +917,7 @@ def run_cfg4(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
     barrier()
     ops.kernel_events = {}
@@ -734,7 +926,7 @@ def run_cfg4(args, rank, world, local_rank):
     with ClockSampler(local_rank) as clocks:
         barrier()
         start.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             step()
         end.record()
         barrier()
@@ -746,51 +938,54 @@ def run_cfg4(args, rank, world, local_rank):
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     elapsed_ms = float(stats[0])
     if rank != 0:
-        return
+        return None
     peak, peak_kind = measured_peak()
     kernels = {}
-    for name, pairs in events.items():
+    for kname, pairs in events.items():
         ms = statistics.mean(a.elapsed_time(b) for a, b in pairs)
         entry = {"ms": ms, "calls": len(pairs)}
-        if name in alg:
-            entry.update(algorithmic_bytes=alg[name], achieved=alg[name] / ms / 1e6, frac=alg[name] / ms / 1e6 / peak)
-        kernels[name] = entry
+        if kname in alg:
+            entry.update(algorithmic_bytes=alg[kname], achieved=alg[kname] / ms / 1e6, frac=alg[kname] / ms / 1e6 / peak)
+        kernels[kname] = entry
     top = max(alg, key=lambda k: kernels[k]["ms"])
 
-    # CPU baseline: the oracle port of the same chain (fp32 arithmetic) on the first 2048 tokens
-    import numpy as np
+    cpu_baseline = None
+    if cpu:  # the oracle port of the same chain (fp32 arithmetic) on the first 2048 tokens
+        import oracle
 
-    import oracle
-
-    oracle.use_all_cores()
-    Ts = min(T, 2048)
-    o_ix = oracle.build_index(idx_cpu[:Ts].numpy(), w_cpu[:Ts].numpy(), E)
-    xs = x.detach()[:Ts].float().cpu().numpy()
-    gs = grad_out[:Ts].float().cpu().numpy()
-    t0 = time.perf_counter()
-    perm = oracle.permute(xs, o_ix["reverse_map"])
-    oracle.combine([perm], o_ix["reverse_map"], o_ix["sorted_w"], Ts)
-    g_rows, _ = oracle.combine_bwd(perm, o_ix["reverse_map"], o_ix["sorted_w"], gs)
-    oracle.permute_bwd(g_rows, o_ix["reverse_map"], Ts)
-    cpu_s = time.perf_counter() - t0
-    cpu_baseline = {"value": total_bytes * Ts / T / cpu_s / 1e9, "unit": UNIT, "cores": oracle.num_threads(),
-                    "kind": "port", "ms": cpu_s * 1e3,
-                    "sample": f"the first {Ts} of {T} tokens, one pass of permute + combine + both backwards "
-                              "in fp32; bytes counted as in the bf16 workload"}  # fmt: skip
-    del np
-    line = {
-        "metric": "dispatch_combine_hbm_gbs", "value": total_bytes * world * args.steps / (elapsed_ms / 1e3) / 1e9,
-        "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        oracle.use_all_cores()
+        Ts = min(T, 2048)
+        o_ix = oracle.build_index(idx_cpu[:Ts].numpy(), w_cpu[:Ts].numpy(), E)
+        xs = x.detach()[:Ts].float().cpu().numpy()
+        gs = grad_out[:Ts].float().cpu().numpy()
+        t0 = time.perf_counter()
+        perm = oracle.permute(xs, o_ix["reverse_map"])
+        oracle.combine([perm], o_ix["reverse_map"], o_ix["sorted_w"], Ts)
+        g_rows, _ = oracle.combine_bwd(perm, o_ix["reverse_map"], o_ix["sorted_w"], gs)
+        oracle.permute_bwd(g_rows, o_ix["reverse_map"], Ts)
+        cpu_s = time.perf_counter() - t0
+        cpu_baseline = {"value": total_bytes * Ts / T / cpu_s / 1e9, "unit": UNIT, "cores": oracle.num_threads(),
+                        "kind": "port", "ms": cpu_s * 1e3,
+                        "sample": f"the first {Ts} of {T} tokens, one pass of permute + combine + both backwards "
+                                  "in fp32; bytes counted as in the bf16 workload"}  # fmt: skip
+    return {
+        "metric": "dispatch_combine_hbm_gbs", "value": total_bytes * world * steps / (elapsed_ms / 1e3) / 1e9,
+        "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": max(warmup, 3),
+        "ms_per_step": elapsed_ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "T": T, "D": D, "E": E, "top_k": K, "routing": "uniform",
-                   "l2": "inputs (1.9 GB of routed rows) exceed the 126 MB L2", "multi_gpu": "replicas only"},
+        "config": {"workload": name, "T": T, "D": D, "E": E, "top_k": K, "routing": "uniform"},
+        "notes": {"l2": "inputs (1.9 GB of routed rows) exceed the 126 MB L2", "multi_gpu": "replicas only"},
         "e2e": None, "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": top, "achieved": kernels[top]["achieved"], "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": kernels[top]["frac"], "traffic": None},
         "kernels": kernels, "cpu_baseline": cpu_baseline, "clocks": clocks.summary(),
     }  # fmt: skip
-    print(json.dumps(line), flush=True)
+
+
+def run_cfg4(args, rank, world, local_rank):
+    line = cfg4_record(args.workload, rank, world, local_rank, args.steps, args.warmup)
+    if line is not None:
+        print(json.dumps(line), flush=True)
 
 
 def main():
@@ -805,6 +1000,9 @@ def main():
                     help="expert-parallel layer with several ranks: fused peer-store exchange or NCCL all-to-all")
     ap.add_argument("--gemm-sms", type=int, default=None, help="expert-parallel layer: SMs for the grouped GEMM")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel layer part of the default run")
+    ap.add_argument("--no-also", action="store_true", help="skip the skewed-combine and dispatch+combine sub-records")
+    ap.add_argument("--cpu-port", action="store_true",
+                    help="CPU baseline: time the C port even where the reference package is installed")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="launch-shape knob of the library (fmoe_tune), for sweeps; repeatable")
     args = ap.parse_args()

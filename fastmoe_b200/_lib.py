@@ -39,6 +39,8 @@ SIGNATURES = {
     "fmoe_combine_gather": (c_int, [_P, _P, _L, _L, _L, _L, _I, _I, _P]),
     "fmoe_combine_fwd_static": (c_int, [_P, _P, _P, _P, _I, _P, _I, _P, _L, _L, _L, _L, _L, _I, _I, _P, _P]),
     "fmoe_combine_bwd": (c_int, [_P, _P, _L, _P, _P, _L, _L, _L, _I, _P]),
+    "fmoe_combine_routed": (c_int, [_P, _P, _P, _I, _P, _L, _L, _L, _L, _I, _I, _P]),
+    "fmoe_combine_routed_bwd": (c_int, [_P, _P, _P, _I, _P, _L, _P, _P, _L, _L, _L, _I, _P]),
     "fmoe_route_topk": (c_int, [_P, _I, _L, _L, _L, _P, _P, _I, _P]),
     "fmoe_build_index_bytes": (c_size_t, [_L, _L, _L]),
     "fmoe_build_index": (c_int, [_P, _P, _I, _L, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P, _P]),

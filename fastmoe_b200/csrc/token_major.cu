@@ -111,6 +111,26 @@ struct SlotSource {  // K rows of one matrix per token, unit weights
   }
 };
 
+struct WeightedSlotSource {  // K rows of one matrix per token, each scaled by the gate weight of its slot
+  const int32_t* slot_of;
+  const char* base;
+  const void* w;  // [rows] gate weight per sorted slot
+  int64_t row_bytes;
+  int64_t rows;
+  int K;
+  int w_dtype;
+  __device__ __forceinline__ void segment(int64_t t, int& beg, int& end) const {
+    beg = static_cast<int>(t * K);
+    end = beg + K;
+  }
+  __device__ __forceinline__ void row(int j, const char*& p, float& wt) const {
+    const int32_t s = slot_of[j];
+    const bool ok = s >= 0 && s < rows;
+    p = ok ? base + s * row_bytes : nullptr;
+    wt = ok ? load_scalar_as_float(w, s, w_dtype) : 0.f;
+  }
+};
+
 template <int DT>
 __device__ __forceinline__ uint4 load_row_vec(const char* p, int64_t col) {
   using El = Elem<DT>;
@@ -273,11 +293,41 @@ static int launch_gather_sum(const Source& src, void* out, int64_t out_row_strid
 // tokens per step so that its 8 warps stay busy when tokens have fewer than 8 rows.
 constexpr int kBwdWarps = 8;
 
-template <int DT, bool WITH_GW>
+// What the backward walks: per token a run of entries, per entry the routed row it stands
+// for (g: its row in grad_rows and grad_w), the forward source row and the gate weight.
+struct PlanBwdSource {  // the combine plan: entries are the plan's slots
+  const int32_t* seg_off;
+  const int32_t* row_of_slot;
+  const int64_t* src_sorted;
+  const float* w_sorted;
+  __device__ __forceinline__ int first(int64_t t) const { return seg_off[t]; }
+  __device__ __forceinline__ bool entry(int j, int64_t& g, const char*& p, float& w) const {
+    g = row_of_slot[j];
+    w = w_sorted[j];
+    p = reinterpret_cast<const char*>(src_sorted[j]);
+    return true;
+  }
+};
+struct SlotBwdSource {  // the routing index: entry t*K+k is routed copy k of token t, at sorted slot slot_of[t*K+k]
+  const int32_t* slot_of;
+  const char* base;  // the forward's rows, one per sorted slot
+  const void* w;
+  int64_t row_bytes, rows;
+  int K, w_dtype;
+  __device__ __forceinline__ int first(int64_t t) const { return static_cast<int>(t * K); }
+  __device__ __forceinline__ bool entry(int j, int64_t& g, const char*& p, float& wt) const {
+    const int32_t s = slot_of[j];
+    if (s < 0 || s >= rows) return false;
+    g = s;
+    p = base + s * row_bytes;
+    wt = load_scalar_as_float(w, s, w_dtype);
+    return true;
+  }
+};
+
+template <int DT, bool WITH_GW, class Source>
 __global__ void __launch_bounds__(kBwdWarps * 32)
-    combine_bwd_kernel(const int32_t* __restrict__ seg_off, const int32_t* __restrict__ row_of_slot,
-                       const int64_t* __restrict__ src_sorted, const float* __restrict__ w_sorted,
-                       const void* __restrict__ grad_out, int64_t go_row_stride,
+    combine_bwd_kernel(const Source src, const void* __restrict__ grad_out, int64_t go_row_stride,
                        void* __restrict__ grad_rows, float* __restrict__ grad_w, int64_t T,
                        int64_t D, int64_t dvec, int group) {
   using El = Elem<DT>;
@@ -289,13 +339,14 @@ __global__ void __launch_bounds__(kBwdWarps * 32)
   for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
     const int64_t t0 = item * group;
     const int64_t t1 = min(T, t0 + group);
-    const int beg = seg_off[t0], end = seg_off[t1];
+    const int beg = src.first(t0), end = src.first(t1);
     int64_t t = t0;
     for (int j = beg + warp; j < end; j += kBwdWarps) {
-      while (t + 1 < t1 && seg_off[t + 1] <= j) ++t;  // token that owns slot j
-      const int64_t g = row_of_slot[j];
-      const float w = w_sorted[j];
-      const char* p = reinterpret_cast<const char*>(src_sorted[j]);
+      while (t + 1 < t1 && src.first(t + 1) <= j) ++t;  // token that owns entry j
+      int64_t g;
+      float w;
+      const char* p;
+      if (!src.entry(j, g, p, w)) continue;
       const uint4* gorow =
           reinterpret_cast<const uint4*>(reinterpret_cast<const Ty*>(grad_out) + t * go_row_stride);
       uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<Ty*>(grad_rows) + g * D);
@@ -508,10 +559,10 @@ extern "C" int fmoe_combine_bwd(const void* plan, const void* grad_out, int64_t 
   if (group > kBwdWarps) group = kBwdWarps;
   const int grid = static_cast<int>(clamp_grid((T + group - 1) / group, g_bwd_ctas_per_sm));
   int rc = 0;
-#define FMOE_BWD_LAUNCH(DT, GW)                                                               \
-  combine_bwd_kernel<DT, GW><<<grid, kBwdWarps * 32, 0, s>>>(                                 \
-      pv.seg_off, pv.row_of_slot, pv.src_sorted, pv.w_sorted, grad_out, grad_out_row_stride,  \
-      grad_rows, grad_w, T, D, dvec, group)
+  const PlanBwdSource src{pv.seg_off, pv.row_of_slot, pv.src_sorted, pv.w_sorted};
+#define FMOE_BWD_LAUNCH(DT, GW)                                                    \
+  combine_bwd_kernel<DT, GW, PlanBwdSource><<<grid, kBwdWarps * 32, 0, s>>>(       \
+      src, grad_out, grad_out_row_stride, grad_rows, grad_w, T, D, dvec, group)
   FMOE_DISPATCH_DTYPE(dtype, DT, {
     if (grad_w) FMOE_BWD_LAUNCH(DT, true); else FMOE_BWD_LAUNCH(DT, false);
     rc = check_launch("combine_bwd_kernel");
@@ -580,6 +631,67 @@ extern "C" int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_o
   FMOE_DISPATCH_DTYPE(dtype, DT,
                       rc = (launch_gather_sum<DT, false, SlotSource>(src, grad_x, grad_x_row_stride,
                                                                      T, D, 0, s)));
+  return rc;
+}
+
+// ---- combine straight from the routing index (no plan) -----------------------------------------
+extern "C" int fmoe_combine_routed(const void* rows, const int32_t* slot_of, const void* w_sorted, int w_dtype,
+                                   void* out, int64_t out_row_stride, int64_t T, int64_t K, int64_t D, int dtype,
+                                   int accumulate, void* stream) {
+  FMOE_REQUIRE(valid_dtype(dtype) && valid_dtype(w_dtype), FMOE_ERR_ARG, "fmoe_combine_routed: bad dtype %d / %d",
+               dtype, w_dtype);
+  FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_combine_routed: negative size");
+  FMOE_REQUIRE(T * K < (1ll << 31), FMOE_ERR_UNSUPPORTED, "fmoe_combine_routed: T*K must fit in int32");
+  if (T == 0 || D == 0) return FMOE_OK;
+  FMOE_REQUIRE(out != nullptr, FMOE_ERR_ARG, "fmoe_combine_routed: out is null");
+  FMOE_REQUIRE(K == 0 || (rows && slot_of && w_sorted), FMOE_ERR_ARG, "fmoe_combine_routed: null pointer argument");
+  FMOE_REQUIRE(out_row_stride >= D, FMOE_ERR_ARG, "fmoe_combine_routed: out_row_stride < D");
+  const WeightedSlotSource src{slot_of, static_cast<const char*>(rows), w_sorted,
+                               D * static_cast<int64_t>(dtype_size(dtype)), T * K, static_cast<int>(K), w_dtype};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = 0;
+  FMOE_DISPATCH_DTYPE(dtype, DT,
+                      rc = (launch_gather_sum<DT, true, WeightedSlotSource>(src, out, out_row_stride, T, D,
+                                                                            accumulate != 0, s)));
+  return rc;
+}
+
+extern "C" int fmoe_combine_routed_bwd(const void* rows, const int32_t* slot_of, const void* w_sorted, int w_dtype,
+                                       const void* grad_out, int64_t grad_out_row_stride, void* grad_rows,
+                                       float* grad_w, int64_t T, int64_t K, int64_t D, int dtype, void* stream) {
+  FMOE_REQUIRE(valid_dtype(dtype) && valid_dtype(w_dtype), FMOE_ERR_ARG,
+               "fmoe_combine_routed_bwd: bad dtype %d / %d", dtype, w_dtype);
+  FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_combine_routed_bwd: negative size");
+  FMOE_REQUIRE(T * K < (1ll << 31), FMOE_ERR_UNSUPPORTED, "fmoe_combine_routed_bwd: T*K must fit in int32");
+  const int64_t N = T * K;
+  if (N == 0) return FMOE_OK;
+  FMOE_REQUIRE(slot_of && w_sorted && grad_out && grad_rows && (grad_w == nullptr || rows != nullptr), FMOE_ERR_ARG,
+               "fmoe_combine_routed_bwd: null pointer argument");
+  FMOE_REQUIRE(grad_out_row_stride >= D, FMOE_ERR_ARG, "fmoe_combine_routed_bwd: grad_out_row_stride < D");
+  const int eb = dtype_size(dtype);
+  const int kvec = 16 / eb;
+  FMOE_REQUIRE(D % kvec == 0 && aligned_to(grad_out, 16) && aligned_to(grad_rows, 16) && aligned_to(rows, 16) &&
+                   (grad_out_row_stride * eb) % 16 == 0,
+               FMOE_ERR_UNSUPPORTED,
+               "fmoe_combine_routed_bwd: D must be a multiple of %d and buffers 16-byte aligned", kvec);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (grad_w != nullptr) FMOE_CUDA(cudaMemsetAsync(grad_w, 0, sizeof(float) * N, s));  // slots no token names
+  if (D == 0) return FMOE_OK;
+  const int64_t dvec = D / kvec;
+  int group = static_cast<int>(K >= kBwdWarps ? 1 : (kBwdWarps + K - 1) / K);
+  if (group > kBwdWarps) group = kBwdWarps;
+  const int grid = static_cast<int>(clamp_grid((T + group - 1) / group, g_bwd_ctas_per_sm));
+  const SlotBwdSource src{slot_of, static_cast<const char*>(rows), w_sorted, D * static_cast<int64_t>(eb), N,
+                          static_cast<int>(K), w_dtype};
+  int rc = 0;
+#define FMOE_BWD_LAUNCH(DT, GW)                                                  \
+  combine_bwd_kernel<DT, GW, SlotBwdSource><<<grid, kBwdWarps * 32, 0, s>>>(     \
+      src, grad_out, grad_out_row_stride, grad_rows, grad_w, T, D, dvec, group)
+  FMOE_DISPATCH_DTYPE(dtype, DT, {
+    if (grad_w) FMOE_BWD_LAUNCH(DT, true); else FMOE_BWD_LAUNCH(DT, false);
+    rc = check_launch("combine_bwd_kernel (routed)");
+  });
+#undef FMOE_BWD_LAUNCH
   return rc;
 }
 

@@ -42,7 +42,7 @@ import torch.distributed as dist
 
 from . import _lib
 from .kernels import experts, ops, routing
-from .kernels.ops import _DTYPES, _status_word, _stream_ptr, grouped_weighted_scatter_add
+from .kernels.ops import _DTYPES, _status_word, _stream_ptr, routed_combine
 
 
 @dataclass
@@ -261,8 +261,7 @@ class FusedExpertParallel:
         topk_w, topk_idx = routing.route_topk(moe.router(x_flat), K, w_dtype=x.dtype)
         ix = routing.build_index(topk_idx, topk_w, moe.num_experts, self.world)
         rows = self.experts_over_peers(x_flat, topk_idx, ix)
-        out = grouped_weighted_scatter_add([rows], ix.reverse_map, ix.sorted_w, (n_tok, D))
-        return out.view(B, T, D)
+        return routed_combine(rows, ix.slot_of, ix.sorted_w, K).view(B, T, D)
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -278,8 +277,7 @@ class FusedExpertParallel:
         lay = self._layout(ix.counts)
         self._exchange_and_experts(x_flat, topk_idx, ix, lay)
         ret = self._ret.view(self.max_rows, D)[: n_tok * K]
-        out = grouped_weighted_scatter_add([ret], ix.reverse_map, ix.sorted_w, (n_tok, D))
-        return out.view(B, T, D)
+        return routed_combine(ret, ix.slot_of, ix.sorted_w, K).view(B, T, D)
 
     __call__ = forward
 

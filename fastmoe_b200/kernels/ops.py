@@ -35,6 +35,7 @@ __all__ = [
     "GroupedMetadata",
     "CombinePlan",
     "build_combine_plan",
+    "routed_combine",
     "combine_mode",
     "set_combine_mode",
     "read_status",
@@ -46,6 +47,7 @@ _size = torch.Tensor.size
 _data_ptr = torch.Tensor.data_ptr
 _dtype = operator.attrgetter("dtype")
 _get_device = torch.Tensor.get_device
+_requires_grad = operator.attrgetter("requires_grad")
 _head = operator.itemgetter(0)
 
 # The reference exports this flag (ops.py:10,12); this build never uses Triton.
@@ -246,7 +248,8 @@ class CombinePlan:
 
 
 def build_combine_plan(expert_tensors, indices, weights, n_out, metadata=None) -> CombinePlan:
-    """Builds the plan for out[n_out, D]. Four small launches on the current stream."""
+    """Builds the plan for out[n_out, D]: one cooperative launch on the current stream (four
+    small ones where the sizes rule that out)."""
     metadata = _metadata_for(expert_tensors, indices, metadata)
     ptr_table, chunk_sizes, expert_offsets, _, num_experts = metadata
     n_rows, dim, dtype = metadata.num_rows, metadata.dim, metadata.dtype
@@ -381,6 +384,69 @@ class GroupedWeightedScatterAdd(torch.autograd.Function):
         return None, grad_w, None, *grad_experts
 
 
+class _RoutedCombine(torch.autograd.Function):
+    """out[t] = sum_k rows[slot_of[t*K+k]] * sorted_w[slot_of[t*K+k]]: the combine fed by the
+    routing index itself (no plan), with gradients for the rows and the gate weights."""
+
+    @staticmethod
+    def forward(ctx, rows, slot_of, sorted_w, K):
+        T = slot_of.numel() // K
+        D = rows.shape[1]
+        out = torch.empty(T, D, dtype=rows.dtype, device=rows.device)
+        _call("fmoe_combine_routed", 1, rows.data_ptr(), slot_of.data_ptr(), sorted_w.data_ptr(),
+              _DTYPES[sorted_w.dtype], out.data_ptr(), D, T, K, D, _DTYPES[rows.dtype], 0, _stream_ptr(rows.device))  # fmt: skip
+        ctx.save_for_backward(rows, slot_of, sorted_w)
+        ctx.K = K
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        rows, slot_of, sorted_w = ctx.saved_tensors
+        K, (N, D) = ctx.K, rows.shape
+        T = N // K
+        if grad_out.dim() != 2 or (D > 1 and grad_out.stride(1) != 1):
+            grad_out = grad_out.contiguous()
+        if grad_out.dtype != rows.dtype:
+            grad_out = grad_out.to(rows.dtype)
+        grad_rows = torch.empty_like(rows)
+        want_gw = ctx.needs_input_grad[2]
+        grad_w = torch.empty(N, device=rows.device, dtype=torch.float32) if want_gw else None
+        row_stride = int(grad_out.stride(0)) if T > 1 else D
+        _call("fmoe_combine_routed_bwd", 1, rows.data_ptr(), slot_of.data_ptr(), sorted_w.data_ptr(),
+              _DTYPES[sorted_w.dtype], grad_out.data_ptr(), row_stride, grad_rows.data_ptr(),
+              grad_w.data_ptr() if want_gw else None, T, K, D, _DTYPES[rows.dtype], _stream_ptr(rows.device))  # fmt: skip
+        return grad_rows, None, grad_w.to(sorted_w.dtype) if want_gw else None, None
+
+
+def routed_combine(rows, slot_of, sorted_w, top_k):
+    """The combine for rows that are ONE matrix in the index builder's sorted-slot order:
+    out[t] = sum over k of rows[slot_of[t*K+k]] * sorted_w[slot_of[t*K+k]], [T, D] in the rows'
+    dtype. `slot_of` (int32 [T*K]) is `build_index`'s inverse map, `sorted_w` the gate weight per
+    sorted slot. Equal to `grouped_weighted_scatter_add([rows], reverse_map, sorted_w, (T, D))`
+    up to the order of the K additions per token, without building a plan: inside the layer
+    the index is already in hand (MoEFeedForward.unpermute, src/fastmoe/models/tiny_model.py:
+    396-409). Differentiable in `rows` and `sorted_w`."""
+    _require_cuda(rows, "rows")
+    _require_cuda(slot_of, "slot_of")
+    _require_cuda(sorted_w, "sorted_w")
+    if rows.dim() != 2 or rows.dtype not in _DTYPES or sorted_w.dtype not in _DTYPES:
+        raise ValueError("rows must be a 2-D float32/bfloat16/float16 matrix and sorted_w a float vector")
+    K = int(top_k)
+    N = rows.shape[0]
+    if slot_of.dtype != torch.int32 or slot_of.numel() != N or sorted_w.numel() != N or K < 1 or N % K:
+        raise ValueError(f"slot_of (int32) and sorted_w need one entry per row ({N}), a multiple of top_k={K}")
+    D = rows.shape[1]
+    if D % (16 // rows.element_size()):
+        raise ValueError(f"routed_combine needs a row width that is a multiple of 16 bytes, got D={D}")
+    return _RoutedCombine.apply(rows.contiguous(), slot_of.contiguous(), sorted_w.contiguous(), K)
+
+
+def _needs_grad(expert_tensors, weights):
+    if not torch.is_grad_enabled():
+        return False
+    return weights.requires_grad or any(map(_requires_grad, expert_tensors))
+
+
 def grouped_weighted_scatter_add(expert_tensors, indices, weights, out_shape, out=None, metadata=None):
     """Sums weighted rows of disjoint per-expert matrices into token rows.
 
@@ -392,6 +458,18 @@ def grouped_weighted_scatter_add(expert_tensors, indices, weights, out_shape, ou
     _require_cuda(indices, "indices")
     if out is not None:
         _combine_into(expert_tensors, indices, weights, out, metadata, accumulate=True)
+        return out
+    if not _needs_grad(expert_tensors, weights):
+        # nothing to differentiate: the same launches without handing E tensors to autograd
+        if len(expert_tensors) == 0:
+            raise ValueError("expert_tensors is empty")
+        ref = expert_tensors[0]
+        _require_cuda(ref, "expert_tensors[0]")
+        out_shape = tuple(int(s) for s in out_shape)
+        if len(out_shape) != 2:
+            raise ValueError(f"out_shape must be (T, D), got {out_shape}")
+        out = torch.empty(out_shape, device=ref.device, dtype=ref.dtype)
+        _combine_into(expert_tensors, indices, weights, out, metadata, accumulate=False)
         return out
     return GroupedWeightedScatterAdd.apply(indices, weights, out_shape, *expert_tensors)
 

@@ -34,7 +34,7 @@ from .. import consts, exchange
 from ..kernels import experts as expert_kernels
 from ..kernels import routing
 from ..kernels.experts import grouped_gelu_ffn, grouped_swiglu_ffn
-from ..kernels.ops import grouped_weighted_scatter_add
+from ..kernels.ops import grouped_weighted_scatter_add, routed_combine
 
 
 class MultiheadSelfAttention(nn.Module):
@@ -53,6 +53,19 @@ class MultiheadSelfAttention(nn.Module):
         q, k, v = self.qkv(x).view(B, T, 3, self.n_heads, self.hd).permute(2, 0, 3, 1, 4)
         y = F.scaled_dot_product_attention(q, k, v, is_causal=False)
         return self.proj(y.transpose(1, 2).reshape(B, T, D))
+
+
+class RoutedShape(tuple):
+    """The (B, T) that `gate_and_sort` returns as its last element (tiny_model.py:155-164),
+    carrying the index builder's inverse map `slot_of` (int32 [B*T*top_k]: the sorted slot of
+    routed copy k of token t) to `unpermute`, which can then combine without building a plan."""
+
+    slot_of = None
+
+    def __new__(cls, shape, slot_of=None):
+        self = super().__new__(cls, shape)
+        self.slot_of = slot_of
+        return self
 
 
 class GroupedSwiGLUExperts(nn.Module):
@@ -131,7 +144,7 @@ class MoEFeedForward(nn.Module):
         ix = routing.build_index(topk_idx, topk_w, self.num_experts, self.world_size)
         permuted = routing.permute_rows(x_flat, ix.slot_of, self.top_k)
         by_rank = ix.counts.view(self.world_size, self.num_local_experts)
-        return permuted, ix.rank_counts, by_rank, ix.reverse_map, ix.sorted_w, (B, T)
+        return permuted, ix.rank_counts, by_rank, ix.reverse_map, ix.sorted_w, RoutedShape((B, T), ix.slot_of)
 
     # -- stage 2 ---------------------------------------------------------------------------
     def dispatch_exchange(self, permuted_data, send_rank_counts, send_expert_counts):
@@ -306,6 +319,12 @@ class MoEFeedForward(nn.Module):
             out.index_add_(0, reverse_map_indices, x_out)
             return out.view(B, T, D)
         if self.implementation == consts.MoEImplementation.FAST:
+            slot_of = getattr(original_shape, "slot_of", None)
+            if (torch.is_tensor(x_out) and slot_of is not None and x_out.is_cuda and x_out.dim() == 2
+                    and x_out.shape[0] == slot_of.numel() == sorted_weights.numel()
+                    and x_out.shape[1] % (16 // x_out.element_size()) == 0):  # fmt: skip
+                # one matrix in sorted-slot order and the inverse map in hand: no plan to build
+                return routed_combine(x_out, slot_of, sorted_weights, self.top_k).view(B, T, D)
             experts = list(x_out) if isinstance(x_out, (list, tuple)) else [x_out]
             out = grouped_weighted_scatter_add(experts, reverse_map_indices, sorted_weights, (B * T, D))
             return out.view(B, T, D)

@@ -122,7 +122,9 @@ size_t fmoe_combine_plan_bytes(int64_t N, int64_t T);
 
 /* Builds the plan. Replaces `prepare_grouped_metadata`'s device side
  * (ops.py:200-271) plus the per-row lookups of the Triton kernel
- * (ops.py:129-163). Four small launches, no host synchronisation. */
+ * (ops.py:129-163). One cooperative launch (count, scan, place, resolve, with grid-wide
+ * barriers in between) where the device allows it and the sizes fit, else four small
+ * launches; no host synchronisation either way. */
 int fmoe_combine_plan(const int64_t* ptr_table, const int32_t* chunk_sizes,
                       const int64_t* expert_offsets, const void* idx, int idx_type,
                       const void* w, int w_dtype, int64_t E, int64_t N, int64_t T,
@@ -175,6 +177,25 @@ int fmoe_combine_fwd_static(const int64_t* ptr_table, const int32_t* chunk_sizes
 int fmoe_combine_bwd(const void* plan, const void* grad_out, int64_t grad_out_row_stride,
                      void* grad_rows, float* grad_w, int64_t N, int64_t T, int64_t D,
                      int dtype, void* stream);
+
+/*
+ * The combine straight from the routing index, without a plan: where the rows to be
+ * combined are ONE matrix in sorted-slot order and the index builder's inverse map is at
+ * hand (inside the MoE layer: MoEFeedForward.unpermute, src/fastmoe/models/tiny_model.py:
+ * 396-409, which the reference always calls with one tensor), the plan's counting sort is
+ * redundant: token t's sources are rows slot_of[t*K + k], k < K.
+ *   out[t, :] (=|+=) sum_k rows[slot_of[t*K+k], :] * w_sorted[slot_of[t*K+k]]    (k ascending, fp32)
+ * rows [T*K, D] dtype, row stride D; slot_of int32[T*K]; w_sorted [T*K] w_dtype (the gate
+ * weight of each sorted slot). No scratch memory, one launch, same token-major kernel.
+ * The backward writes grad_rows[s, :] = grad_out[t, :] * w_sorted[s] and (optional, fp32)
+ * grad_w[s] = <grad_out[t, :], rows[s, :]> for s = slot_of[t*K+k].
+ */
+int fmoe_combine_routed(const void* rows, const int32_t* slot_of, const void* w_sorted, int w_dtype,
+                        void* out, int64_t out_row_stride, int64_t T, int64_t K, int64_t D, int dtype,
+                        int accumulate, void* stream);
+int fmoe_combine_routed_bwd(const void* rows, const int32_t* slot_of, const void* w_sorted, int w_dtype,
+                            const void* grad_out, int64_t grad_out_row_stride, void* grad_rows,
+                            float* grad_w, int64_t T, int64_t K, int64_t D, int dtype, void* stream);
 
 /* ---- router: top-k + gate softmax ---------------------------------------- */
 /*

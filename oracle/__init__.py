@@ -6,7 +6,10 @@ plain C (`combine_oracle.c`, loaded through ctypes) and numpy (`routing.py`,
 legs may import it; nothing under fastmoe_b200/ does.
 
 Pinned: every function here is checked against fixtures produced by importing the
-reference itself (tests/golden/make_golden.py, tests/test_oracle_golden.py).
+reference itself (tests/golden/make_golden.py, tests/test_oracle_golden.py). Where a
+checkout of the reference is at hand, `install_ref.py` installs the unmodified package
+into oracle/_ref/ (untracked) and `reference_ops()` hands out its operator module, which
+bench.py times as the CPU baseline and tests compare the C port with.
 
 bf16 data crosses this interface as numpy uint16 bit patterns.
 """
@@ -43,6 +46,27 @@ def _c():
         _lib = ctypes.CDLL(str(build()))
         _lib.oracle_num_threads.restype = ctypes.c_int
     return _lib
+
+
+def reference_ops():
+    """The reference's own operator module (`fastmoe.kernels.ops`, unmodified), if
+    oracle/install_ref.py has installed the package into oracle/_ref/; None where it has not
+    (or where its imports fail). Used to time the reference's CPU path
+    (src/fastmoe/kernels/ops.py:373-384) beside this build's kernels, and to check the C port
+    of that path against the real thing."""
+    ref_dir = _DIR / "_ref"
+    if not (ref_dir / "fastmoe" / "kernels" / "ops.py").exists():
+        return None
+    import importlib
+    import sys
+
+    sys.path.insert(0, str(ref_dir))
+    try:
+        return importlib.import_module("fastmoe.kernels.ops")
+    except Exception:  # a dependency of the package (settings, logging) is missing on this machine
+        return None
+    finally:
+        sys.path.remove(str(ref_dir))
 
 
 def num_threads() -> int:

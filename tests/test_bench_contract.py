@@ -1,4 +1,5 @@
-"""bench.py's reference arm runs without a GPU (it times the CPU port of the reference's path):
+"""bench.py's reference arm runs without a GPU (it times the reference's CPU path: the
+unmodified package where oracle/install_ref.py has installed it, else the C port of it):
 here on a small workload, checking the JSON line the driver parses."""
 
 import json
@@ -6,13 +7,16 @@ import subprocess
 import sys
 from pathlib import Path
 
+import pytest
+
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def test_reference_arm_prints_one_json_line_with_the_contract_keys():
+@pytest.mark.parametrize("extra,kinds", [((), ("reference", "port")), (("--cpu-port",), ("port",))])
+def test_reference_arm_prints_one_json_line_with_the_contract_keys(extra, kinds):
     proc = subprocess.run(
         [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "2", "--warmup", "1",
-         "--workload", "combine_small_bf16_T1024_D4096_E64_top8"],
+         "--workload", "combine_small_bf16_T1024_D4096_E64_top8", *extra],
         capture_output=True, text=True, timeout=300, env={"CUDA_VISIBLE_DEVICES": "", "PATH": "/usr/bin:/bin"},
     )  # fmt: skip
     assert proc.returncode == 0, proc.stderr[-2000:]
@@ -24,7 +28,8 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
                 "data", "config", "cpu_baseline", "e2e"):  # fmt: skip
         assert key in d, key
     assert d["steps"] == 2 and d["value"] > 0 and d["config"]["workload"].startswith("combine_small")
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["kind"] in kinds and d["cpu_baseline"]["cores"] >= 1
+    assert set(d["config"]) == {"workload", "T", "D", "E", "top_k", "routing"}  # the same keys as the GPU arm's
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"]
 
 

@@ -253,3 +253,60 @@ def test_cuda_graph_capture_and_replay_like_the_reference_benchmark():
         assert_close(out_static, ref, torch.float32, f"graph replay / {mode}")
         if mode == "gather":
             assert np.array_equal(to_np(out_static), ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,D,E,K", [(64, 128, 8, 2), (257, 1000, 16, 4), (128, 7168, 32, 8), (33, 8, 4, 1)])
+def test_routed_combine_matches_oracle(dtype, T, D, E, K):
+    """The plan-free combine (one matrix in sorted-slot order + the index builder's inverse map)
+    against the oracle's combine and its backward on the same values: forward, d(rows) and
+    d(gate). It adds a token's K rows in routed order k rather than in ascending row order, so
+    fp32 is held to 1e-5, not to bit equality."""
+    from fastmoe_b200.kernels import routing
+    from fastmoe_b200.workloads import routing_uniform
+
+    idx, w = routing_uniform(T, E, K, seed=T + K)
+    gen = torch.Generator(device=DEV).manual_seed(D)
+    gate = w.to(DEV).to(dtype).requires_grad_(True)
+    ix = routing.build_index(idx.to(DEV), gate, E)
+    rows = torch.randn(T * K, D, generator=gen, device=DEV).to(dtype).requires_grad_(True)
+    grad_out = torch.randn(T, D, generator=gen, device=DEV).to(dtype)
+    out = ops.routed_combine(rows, ix.slot_of, ix.sorted_w, K)
+    out.backward(grad_out)
+    rm = ix.reverse_map.cpu().numpy()
+    sw = to_np(ix.sorted_w)
+    ref = oracle.combine([to_np(rows)], rm, sw, T)
+    assert_close(out, ref, dtype, "out")
+    g_rows, g_w = oracle.combine_bwd(to_np(rows), rm, sw, to_np(grad_out))
+    assert_close(rows.grad, g_rows, dtype, "d(rows)")
+    dgate = np.empty(T * K, np.float32)
+    dgate[:] = g_w[ix.slot_of.cpu().numpy()]
+    assert_close(gate.grad.reshape(-1), dgate, dtype, "d(gate)")
+    # the same numbers as the planned operator gives for this matrix
+    planned = ops.grouped_weighted_scatter_add([rows.detach()], ix.reverse_map, ix.sorted_w.detach(), (T, D))
+    assert_close(out, to_np(planned), dtype, "routed vs planned")
+
+
+def test_routed_combine_refuses_bad_arguments():
+    rows = torch.zeros(8, 16, device=DEV)
+    slot_of = torch.arange(8, device=DEV, dtype=torch.int32)
+    w = torch.ones(8, device=DEV)
+    with pytest.raises(ValueError):
+        ops.routed_combine(rows, slot_of.long(), w, 2)
+    with pytest.raises(ValueError):
+        ops.routed_combine(rows, slot_of[:6], w[:6], 2)
+    with pytest.raises(ValueError):
+        ops.routed_combine(rows, slot_of, w, 3)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.routed_combine(rows.cpu(), slot_of, w, 2)
+
+
+def test_no_grad_call_skips_autograd_but_not_the_work():
+    """Without anything to differentiate the operator launches the same kernels directly
+    (no autograd node holding E tensors); results are identical to the autograd path."""
+    wl = make_combine_workload(T=96, D=256, E=12, K=3, dtype=torch.bfloat16, seed=3, device=DEV)
+    before = ops.launch_count
+    plain = ops.grouped_weighted_scatter_add(wl.experts, wl.indices, wl.weights, (wl.T, wl.D))
+    assert ops.launch_count - before == 2 and not plain.requires_grad
+    tracked = ops.grouped_weighted_scatter_add(wl.experts, wl.indices, wl.weights.clone().requires_grad_(True), (wl.T, wl.D))
+    assert tracked.requires_grad and torch.equal(plain, tracked.detach())

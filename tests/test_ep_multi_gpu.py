@@ -38,7 +38,7 @@ def _worker(rank, world, port, q):
         from fastmoe_b200.kernels import ops, routing
         from fastmoe_b200.models.tiny_model import MoEFeedForward, pipelined_moe_forward
 
-        T, D, FF, E, K = 384, 256, 128, 8, 2
+        T, D, FF, E, K = 384, 256, 256, 8, 2
         moe = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST, expert_type="swiglu").to(dev).bfloat16()
         assert moe.world_size == world and moe.num_local_experts == E // world
         g = torch.Generator(device=dev).manual_seed(7)
@@ -110,7 +110,7 @@ def _fused_worker(rank, world, port, q):
         from fastmoe_b200.kernels import ops
         from fastmoe_b200.models.tiny_model import MoEFeedForward
 
-        T, D, FF, E, K = 640, 256, 128, 8, 2
+        T, D, FF, E, K = 640, 256, 256, 8, 2
         moe = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST, expert_type="swiglu").to(dev).bfloat16()
         g = torch.Generator(device=dev).manual_seed(7)
         with torch.no_grad():
@@ -261,10 +261,10 @@ def _overflow_worker(rank, world, port, q):
         from fastmoe_b200.consts import MoEImplementation
         from fastmoe_b200.ep_fused import FusedExpertParallel
         from fastmoe_b200.kernels import experts, ops, routing
-        from fastmoe_b200.kernels.ops import grouped_weighted_scatter_add
+        from fastmoe_b200.kernels.ops import routed_combine
         from fastmoe_b200.models.tiny_model import MoEFeedForward
 
-        T, D, FF, E, K = 512, 256, 128, 8, 2
+        T, D, FF, E, K = 512, 256, 256, 8, 2
         moe = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST, expert_type="swiglu").to(dev).bfloat16()
         g = torch.Generator(device=dev).manual_seed(7)
         with torch.no_grad():
@@ -291,7 +291,7 @@ def _overflow_worker(rank, world, port, q):
             y = experts.grouped_swiglu_ffn(rows, moe.experts.w_gate_up, moe.experts.w_down, ix.offsets, ix.counts,
                                            covers_all_rows=True)  # fmt: skip
             keep = (torch.arange(T * K, device=dev) < cap).to(y.dtype)
-            return grouped_weighted_scatter_add([y * keep[:, None]], ix.reverse_map, ix.sorted_w * keep, (T, D)).view(1, T, D)
+            return routed_combine(y * keep[:, None], ix.slot_of, ix.sorted_w * keep, K).view(1, T, D)
 
         with torch.no_grad():
             got = small(x)

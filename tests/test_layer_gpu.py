@@ -142,13 +142,47 @@ def test_config4_full_size_identity_property():
     assert ops.read_status() == 0
 
 
+def test_config4_full_size_gate_gradient_against_oracle():
+    """The same full-size configuration with the gate weights as a leaf: d(gate) of every routed
+    copy of a sample of tokens against the oracle's combine backward (the row-wise dot of the
+    upstream gradient with the expert row, which the reference's CPU path yields through
+    autograd), and d(rows) of the same copies, for the planned and for the plan-free combine."""
+    T, D, E, K = 16384, 7168, 256, 8
+    idx, w = routing_uniform(T, E, K, seed=11)
+    gen = torch.Generator(device=DEV).manual_seed(11)
+    x = torch.randn(T, D, generator=gen, device=DEV, dtype=torch.bfloat16)
+    grad_out = torch.randn(T, D, generator=gen, device=DEV, dtype=torch.bfloat16)
+    sample = torch.randperm(T, generator=torch.Generator().manual_seed(12))[:96].sort().values
+    for routed in (False, True):
+        gate = w.to(DEV).bfloat16().requires_grad_(True)
+        ix = routing.build_index(idx.to(DEV), gate, E)
+        permuted = routing.permute_rows(x, ix.slot_of, K).requires_grad_(True)
+        if routed:
+            out = ops.routed_combine(permuted, ix.slot_of, ix.sorted_w, K)
+        else:
+            out = ops.grouped_weighted_scatter_add([permuted], ix.reverse_map, ix.sorted_w, (T, D))
+        out.backward(grad_out)
+        assert ops.read_status() == 0
+        # oracle on the sampled tokens alone: their K rows each, re-indexed to 0..95
+        slots = ix.slot_of.view(T, K)[sample.to(DEV)].reshape(-1).long()
+        rows_s = to_np(permuted.detach()[slots])
+        rm_s = np.repeat(np.arange(sample.numel()), K)
+        w_s = to_np(ix.sorted_w.detach()[slots])
+        g_rows, g_w = oracle.combine_bwd(rows_s, rm_s, w_s, to_np(grad_out[sample.to(DEV)]))
+        assert_close(gate.grad.view(T, K)[sample.to(DEV)].reshape(-1), g_w, torch.bfloat16, f"d(gate), routed={routed}")
+        assert_close(permuted.grad[slots], g_rows, torch.bfloat16, f"d(rows), routed={routed}")
+        out_s = oracle.combine([rows_s], rm_s, w_s, sample.numel())
+        assert_close(out[sample.to(DEV)], out_s, torch.bfloat16, f"out, routed={routed}")
+        del permuted, out
+
+
 @pytest.mark.parametrize("impl", [MoEImplementation.FAST, MoEImplementation.STANDARD])
 def test_swiglu_layer_matches_fp32_reference(impl):
     """SwiGLU experts (the expert-parallel benchmark's FFN): the FAST path runs the tcgen05
     grouped GEMM, the STANDARD path per-expert matrix products; both against a plain PyTorch
     fp32 evaluation of the same layer with the same routing."""
     torch.manual_seed(0)
-    T, D, FF, E, K = 512, 256, 128, 8, 2
+    T, D, FF, E, K = 512, 256, 256, 8, 2
     moe = MoEFeedForward(D, FF, E, K, impl, expert_type="swiglu").to(DEV).bfloat16()
     with torch.no_grad():
         for prm in moe.parameters():
@@ -173,6 +207,40 @@ def test_swiglu_layer_matches_fp32_reference(impl):
     assert err <= 2e-2, err
     assert x.grad is not None and moe.experts.w_gate_up.grad is not None and moe.router.weight.grad is not None
     assert torch.isfinite(x.grad.float()).all()
+
+
+def test_gelu_experts_run_grouped_in_bf16_and_match_the_per_expert_modules():
+    """The reference's own experts (nn.ModuleList of Linear-GELU-Linear, tiny_model.py:68-77):
+    in bf16 the FAST layer runs them as two grouped tcgen05 launches over the stacked weights,
+    the STANDARD layer as a loop of per-expert modules. Same parameters, same inputs: outputs
+    and every gradient (tokens, router, each expert's two matrices) agree within bf16 bounds,
+    the state dict keeps the reference's keys, and an fp32 layer keeps the per-expert path."""
+    torch.manual_seed(3)
+    T, D, FF, E, K = 384, 256, 512, 8, 2
+    fast = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST).to(DEV).bfloat16()
+    std = MoEFeedForward(D, FF, E, K, MoEImplementation.STANDARD).to(DEV).bfloat16()
+    assert "experts.3.0.weight" in fast.state_dict() and "experts.3.2.weight" in fast.state_dict()
+    with torch.no_grad():
+        for prm in fast.parameters():
+            prm.normal_(0, 0.05)
+    std.load_state_dict(fast.state_dict())
+    x = torch.randn(1, T, D, device=DEV).bfloat16()
+    coeff = torch.randn(1, T, D, device=DEV)
+    assert fast._use_grouped(x.view(T, D)) and not std._use_grouped(x.view(T, D))
+    assert not MoEFeedForward(D, FF, E, K, MoEImplementation.FAST).to(DEV)._use_grouped(x.view(T, D).float())
+    results = []
+    for moe in (fast, std):
+        xi = x.clone().requires_grad_(True)
+        before = ops.launch_count
+        out = moe(xi)
+        (out.float() * coeff).sum().backward()
+        results.append((out.detach(), xi.grad, moe.router.weight.grad, moe.experts[0][0].weight.grad,
+                        moe.experts[E - 1][2].weight.grad, ops.launch_count - before))  # fmt: skip
+    assert ops.read_status() == 0
+    for got, want, what in zip(results[0][:5], results[1][:5], ("out", "dx", "d router", "d fc1[0]", "d fc2[-1]")):
+        err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+        assert err <= 3e-2, (what, err)  # two bf16 pipelines against each other
+    assert results[0][5] > results[1][5]  # the FAST layer's kernels are this library's
 
 
 def test_pipelined_block_matches_unpipelined_computation():

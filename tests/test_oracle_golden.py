@@ -126,3 +126,31 @@ def test_layer_cfg1_forward(golden):
     assert abs(checksum - float(g["input_checksum"])) < 1e-9
     out, _ = oracle.moe_layer_forward(x, router, list(w1), list(w2), K=2)
     np.testing.assert_allclose(out, g["out"], rtol=1e-5, atol=1e-6)
+
+
+def test_c_port_matches_the_installed_reference_package():
+    """Where oracle/install_ref.py has installed the unmodified reference package, the C port
+    of its CPU combine is compared with the package itself on fresh random inputs: fp32 to
+    1e-6 of the largest magnitude, bf16 bit for bit (same per-call fp32 accumulation and
+    rounding). Skipped where the package is not installed (it does not travel with the repo)."""
+    import pytest
+    import torch
+
+    import oracle
+
+    ref = oracle.reference_ops()
+    if ref is None:
+        pytest.skip("the reference package is not installed under oracle/_ref")
+    g = torch.Generator().manual_seed(5)
+    T, D, sizes = 37, 24, [5, 0, 11, 3, 20]
+    experts = [torch.randn(n, D, generator=g) for n in sizes]
+    idx = torch.randint(0, T, (sum(sizes),), generator=g)
+    w = torch.rand(sum(sizes), generator=g)
+    want = ref.grouped_weighted_scatter_add(experts, idx, w, (T, D)).numpy()
+    got = oracle.combine([e.numpy() for e in experts], idx.numpy(), w.numpy(), T)
+    assert np.abs(got - want).max() <= 1e-6 * np.abs(want).max()
+    ex16, w16 = [e.bfloat16() for e in experts], w.bfloat16()
+    want16 = ref.grouped_weighted_scatter_add(ex16, idx, w16, (T, D))
+    bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)  # noqa: E731
+    got16 = oracle.combine_bf16([bits(e) for e in ex16], idx.numpy(), bits(w16), T)
+    assert np.array_equal(got16, bits(want16))
