@@ -694,6 +694,305 @@ done:
   }
 }
 
+// ---- tokens as the MMA's N dimension ----------------------------------------------------------
+// The same product with the operands' roles exchanged: 128 WEIGHT rows are the MMA's M dimension
+// (the lanes of tensor memory) and an expert's TOKEN rows are its N dimension, which comes in
+// steps of 16 instead of blocks of 128. An expert with n <= 256 rows is ONE tile of round16(n)
+// tokens; a larger one is cut into ceil(n / 256) tiles of equal size (never a full tile plus a
+// sliver: a sliver would pull a whole weight tile through the SM for a fraction of the work).
+// With a few hundred rows per expert (256 experts on one GPU) this issues 3% more MMA work
+// than the rows need, where 128-row blocks issue 25% more. Operand bytes per MMA are the same
+// as in the kernel above. The accumulator arrives transposed (lane = output column, column =
+// token), so the epilogue turns 32-token chunks around through shared memory and stores whole
+// row segments. Tokens are loaded in 64-row boxes (up to four per stage, each issued by its own
+// lane of warp 0; rows past the tile's end ride along unused: the TMA unit's cost is per box,
+// and boxes of 16 rows measured 2x slower overall). For SwiGLU a tile holds 64 gate rows and
+// the 64 up rows of the same columns; the two factors of a column sit in different warps'
+// lanes of tensor memory and meet in shared memory on their way out.
+struct TnArgs {
+  const int64_t* offsets;
+  const int64_t* counts;
+  const int64_t* c_row_map;
+  const int64_t* c_row_ptrs;
+  __nv_bfloat16* C;
+  int64_t ldc, R;
+  int E;
+  int m_blocks;           // weight tiles per expert: N / 128, or ff / 64 for SwiGLU
+  int k_blocks;           // K / 64
+  int w_rows_per_expert;  // N (2 * ff for SwiGLU)
+  int ff;                 // SwiGLU: row of the first "up" weight inside an expert
+  int swiglu, gelu;
+  int skip_loads;
+  uint32_t spin_limit;
+  int32_t* status;
+};
+
+constexpr int kTnTokens = 256;                   // most tokens in one tile
+constexpr int kTnBox = 16;                       // step of a tile's token count (the MMA's N)
+constexpr int kTnLoadRows = 64;                  // token rows per TMA box
+constexpr int kTnLoadBytes = kTnLoadRows * kBK * 2;  // 8 KB
+constexpr int kTnWBytes = 128 * kBK * 2;         // 16 KB of weights per stage
+constexpr int kTnTBytes = kTnTokens * kBK * 2;   // up to 32 KB of tokens per stage
+constexpr int kTnEpiBytes = 24576;  // epilogue: [2][32][128] bf16 out, or for SwiGLU [2][32][64] bf16 out + [2][32][64] fp32 up
+
+struct TnTile {
+  int expert, mb, rows, n;  // rows = valid tokens, n = rows rounded up to 16 (the MMA's N)
+  int64_t row0;             // first token row in A / C
+};
+
+__device__ __forceinline__ int tn_splits(int64_t n) { return static_cast<int>((n + kTnTokens - 1) / kTnTokens); }
+
+__device__ __forceinline__ TnTile tn_locate(int tile, const int* split_prefix, const TnArgs& a) {
+  int lo = 0, hi = a.E;  // last e with split_prefix[e] * m_blocks <= tile
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (static_cast<int64_t>(split_prefix[mid]) * a.m_blocks <= tile) lo = mid; else hi = mid;
+  }
+  TnTile c;
+  c.expert = lo;
+  const int splits = split_prefix[lo + 1] - split_prefix[lo];
+  const int local = tile - split_prefix[lo] * a.m_blocks;
+  c.mb = local / splits;
+  const int sp = local - c.mb * splits;
+  const int64_t n = expert_rows(a.offsets, a.counts, a.R, lo);
+  const int64_t per = ((n + splits - 1) / splits + kTnBox - 1) / kTnBox * kTnBox;  // equal shares, in whole boxes
+  const int64_t begin = sp * per;
+  int64_t rows = n - begin;
+  rows = rows < 0 ? 0 : (rows < per ? rows : per);
+  c.rows = static_cast<int>(rows);
+  c.n = static_cast<int>((rows + kTnBox - 1) / kTnBox * kTnBox);
+  if (c.n == 0) c.n = kTnBox;
+  c.row0 = a.offsets[lo] + begin;
+  return c;
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// All 128 epilogue threads learn whether every one of them got through its wait.
+__device__ __forceinline__ bool epi_all(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(ok ? 1u : 0u)
+      : "memory");
+  return r != 0;
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    grouped_gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                           const TnArgs a) {  // map_a: box 64 x 64 token rows; map_w: box 64 x 128 (64 x 64 for SwiGLU)
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_w = smem;
+  uint8_t* smem_t = smem + kStages * kTnWBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty = full + kStages;
+  uint64_t* tmem_full = empty + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  int* abort_flag = reinterpret_cast<int*>(tmem_base_slot + 1);
+  uint64_t* drain = reinterpret_cast<uint64_t*>(abort_flag + 1);
+  __nv_bfloat16* turn = reinterpret_cast<__nv_bfloat16*>(smem + kStages * kStageBytes + 256);  // [2][32 tokens][128 cols]
+  float* up_buf = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256 + 8192);  // SwiGLU: [2][32 tokens][64 cols]
+  int* split_prefix = reinterpret_cast<int*>(smem + kStages * kStageBytes + 256 + kTnEpiBytes);  // [E + 1]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int fills = 0;
+  bool mma_issued = false;
+
+  for (int e = threadIdx.x; e < a.E; e += kGemmThreads) {
+    const int64_t n = expert_rows(a.offsets, a.counts, a.R, e);
+    if (n != a.counts[e] && a.counts[e] > 0 && a.status != nullptr && blockIdx.x == 0)
+      atomicOr(a.status, FMOE_STATUS_BAD_EXPERT);
+    split_prefix[e + 1] = tn_splits(n);
+  }
+  if (threadIdx.x == 0) {
+    split_prefix[0] = 0;
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    mbar_init(drain, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < a.E; base += 32) {
+      const int e = base + lane;
+      int v = e < a.E ? split_prefix[e + 1] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += n;
+      }
+      if (e < a.E) split_prefix[e + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_base_slot))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int total_tiles = split_prefix[a.E] * a.m_blocks;
+
+  if (warp == 0) {
+    // ---- TMA producer: lane 0 waits and announces the bytes, every lane issues its boxes ------
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !a.skip_loads; tile += gridDim.x) {
+      const TnTile c = tn_locate(tile, split_prefix, a);
+      const int boxes = (c.n + kTnLoadRows - 1) / kTnLoadRows;
+      const int w_row = c.expert * a.w_rows_per_expert;
+      for (int kb = 0; kb < a.k_blocks; ++kb) {
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, a.spin_limit) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) goto timed_out;
+        if (lane == 0) {
+          mbar_expect_tx(&full[stage], kTnWBytes + boxes * kTnLoadBytes);
+          ++fills;
+        }
+        __syncwarp();
+        if (a.swiglu) {
+          if (lane < 2)  // 64 gate rows (lanes 0-63 of tensor memory), then the 64 up rows of the same columns
+            tma_load_2d(smem_w + stage * kTnWBytes + lane * (kTnWBytes / 2), &map_w, kb * kBK,
+                        w_row + (lane ? a.ff : 0) + c.mb * 64, &full[stage]);
+        } else if (lane == 0) {
+          tma_load_2d(smem_w + stage * kTnWBytes, &map_w, kb * kBK, w_row + c.mb * 128, &full[stage]);
+        }
+        if (lane >= 8 && lane - 8 < boxes)
+          tma_load_2d(smem_t + stage * kTnTBytes + (lane - 8) * kTnLoadBytes, &map_a, kb * kBK,
+                      static_cast<int>(c.row0) + (lane - 8) * kTnLoadRows, &full[stage]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ---------------------------------------------------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const TnTile c = tn_locate(tile, split_prefix, a);
+      // D fp32, A and B bf16, both K-major, M = 128 weight rows, N = this tile's tokens
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(c.n >> 3) << 17) |
+                             (static_cast<uint32_t>(128 >> 4) << 24);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
+      tcgen05_fence_after();
+      const uint32_t tmem_d = tmem_base + acc * kTnTokens;
+      for (int kb = 0; kb < a.k_blocks; ++kb) {
+        if (!mbar_wait(&full[stage], phase, abort_flag, a.spin_limit)) goto timed_out;
+        tcgen05_fence_after();
+        mma_issued = true;
+        const uint64_t dw = smem_desc(smem_u32(smem_w + stage * kTnWBytes));
+        const uint64_t dt = smem_desc(smem_u32(smem_t + stage * kTnTBytes));
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) umma_bf16(tmem_d, dw + 2 * k, dt + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        umma_commit(&empty[stage]);
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      umma_commit(&tmem_full[acc]);
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue: lane = output column, TMEM column = token -----------------------------------
+    const int quarter = warp & 3;
+    const int tid = threadIdx.x - 64;                  // 0..127 among the epilogue threads
+    const int out_cols = a.swiglu ? 64 : 128;          // output columns of one tile
+    const int pieces = out_cols / 8;                   // 16-byte pieces per token row
+    int it = 0;
+    uint32_t chunk = 0;  // running count of 32-token chunks: its parity picks the turning buffer
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const TnTile c = tn_locate(tile, split_prefix, a);
+      const bool got = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, a.spin_limit);
+      if (!epi_all(got)) goto timed_out;  // the four warps go on, or give up, together
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + acc * kTnTokens + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < c.n; c0 += 32, ++chunk) {
+        __nv_bfloat16* buf = turn + (chunk & 1) * (32 * 128);
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        tmem_ld_wait();
+        if (a.swiglu) {
+          // quarters 2 and 3 hold the up factors of the columns whose gate factors quarters 0 and 1 hold
+          float* ups = up_buf + (chunk & 1) * (32 * 64);
+          if (quarter >= 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ups[j * 64 + (quarter - 2) * 32 + lane] = __uint_as_float(r[j]);
+          }
+          epi_bar_sync();
+          if (quarter < 2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int at = j * 64 + quarter * 32 + lane;
+              buf[at] = __float2bfloat16_rn(silu(__uint_as_float(r[j])) * ups[at]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = __uint_as_float(r[j]);
+            buf[j * 128 + quarter * 32 + lane] = __float2bfloat16_rn(a.gelu ? gelu_erf(v) : v);
+          }
+        }
+        epi_bar_sync();  // the chunk is complete in shared memory (the other buffer is being refilled next)
+        const int rows_per_pass = 128 / pieces;
+        for (int r0 = 0; r0 < 32; r0 += rows_per_pass) {
+          const int tr = r0 + tid / pieces, q = tid % pieces;
+          const int token = c0 + tr;
+          const int64_t a_row = c.row0 + token;
+          if (token < c.rows && a_row < a.R) {
+            char* row = nullptr;
+            if (a.c_row_ptrs != nullptr) row = reinterpret_cast<char*>(a.c_row_ptrs[a_row]);
+            if (row == nullptr && a.C != nullptr) {
+              const int64_t out_row = (a.c_row_ptrs == nullptr && a.c_row_map != nullptr) ? a.c_row_map[a_row] : a_row;
+              row = reinterpret_cast<char*>(a.C + out_row * a.ldc);
+            }
+            if (row != nullptr) {
+              const uint4 val = *reinterpret_cast<const uint4*>(buf + tr * out_cols + q * 8);
+              *reinterpret_cast<uint4*>(row + (static_cast<int64_t>(c.mb) * out_cols + q * 8) * 2) = val;
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+  goto done;
+
+timed_out:
+  *abort_flag = 1;
+  if (a.status != nullptr) atomicOr(a.status, FMOE_STATUS_WAIT_TIMEOUT);
+
+done:
+  drain_on_exit(warp, lane, fills, mma_issued, full, drain, abort_flag, kStages, a.spin_limit);
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------
 // SMs the persistent grid may occupy (fmoe_tune "gemm_sms"). Leaving a few SMs free lets
 // NCCL's copy kernels run beside the GEMM instead of waiting for its CTAs to retire.
@@ -709,6 +1008,12 @@ int g_gemm_skip_loads = 0;
 int g_gemm_prefetch = 0;
 static int prefetch_depth(int64_t, int64_t) { return g_gemm_prefetch > 0 ? g_gemm_prefetch : 0; }
 int g_gemm_spin_limit = static_cast<int>(kSpinLimit);
+// fmoe_tune "gemm_tokens_as_n": which forward kernel fmoe_grouped_gemm launches. 1 = tokens as
+// the MMA's N dimension (grouped_gemm_tn_kernel), 0 = tokens in 128-row blocks as its M dimension
+// (grouped_gemm_kernel), -1 = choose from the sizes the host knows: tokens as N while the experts
+// average fewer than kTnAutoRows rows, where padding to 128-row blocks costs most.
+int g_gemm_tokens_as_n = -1;
+constexpr int64_t kTnAutoRows = 0;  // rows per expert below which "auto" picks tokens-as-N (0: never)
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -775,6 +1080,41 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
                "fmoe_grouped_gemm: null pointer argument");
   FMOE_REQUIRE(aligned_to(a, 16) && aligned_to(w, 16) && aligned_to(c, 16), FMOE_ERR_ARG,
                "fmoe_grouped_gemm: a, w and c must be 16-byte aligned");
+  const bool tokens_as_n = g_gemm_tokens_as_n == 1 || (g_gemm_tokens_as_n < 0 && R / E < kTnAutoRows);
+  if (tokens_as_n) {
+    CUtensorMap map_t, map_wt;
+    int rc_t = make_map(&map_t, a, R, K, "A (64-row boxes)", kTnLoadRows);
+    if (rc_t != 0) return rc_t;
+    rc_t = make_map(&map_wt, w, E * N, K, "W", swiglu ? 64 : 128);
+    if (rc_t != 0) return rc_t;
+    TnArgs t;
+    t.offsets = offsets;
+    t.counts = counts;
+    t.c_row_map = c_row_map;
+    t.c_row_ptrs = c_row_ptrs;
+    t.C = static_cast<__nv_bfloat16*>(c);
+    t.ldc = swiglu ? N / 2 : N;
+    t.R = R;
+    t.E = static_cast<int>(E);
+    t.m_blocks = static_cast<int>(swiglu ? (N / 2) / 64 : N / 128);
+    t.k_blocks = static_cast<int>(K / kBK);
+    t.w_rows_per_expert = static_cast<int>(N);
+    t.ff = static_cast<int>(N / 2);
+    t.swiglu = swiglu ? 1 : 0;
+    t.gelu = activation == FMOE_ACT_GELU ? 1 : 0;
+    t.skip_loads = g_gemm_skip_loads;
+    t.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
+    t.status = status;
+    const size_t smem_t = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + kTnEpiBytes + sizeof(int) * (E + 2);
+    FMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   1024 + kStages * kStageBytes + 256 + kTnEpiBytes +
+                                       static_cast<int>(sizeof(int)) * (kMaxExperts + 2)));
+    // upper bound of the tile count, known without reading the counts: one partial tile per expert
+    const int64_t max_tiles_t = (R / kTnTokens + E) * t.m_blocks;
+    const int grid_t = static_cast<int>(max_tiles_t < g_gemm_sms ? max_tiles_t : g_gemm_sms);
+    grouped_gemm_tn_kernel<<<grid_t, kGemmThreads, smem_t, static_cast<cudaStream_t>(stream)>>>(map_t, map_wt, t);
+    return check_launch("grouped_gemm_tn_kernel");
+  }
   CUtensorMap map_a, map_w;
   int rc = make_map(&map_a, a, R, K, "A");
   if (rc != 0) return rc;

@@ -21,7 +21,7 @@ static int g_gather_threads = 0;   // threads per CTA, 0 = choose from D
 static int g_gather_ctas_per_sm = -1;  // persistent grid = 148 * this; 0 = one CTA per item; -1 = auto
 static int g_bwd_ctas_per_sm = 3;
 int g_host_chunks = 1;  // column slices of fmoe_combine_host (host_api.cu); 0 = choose from the sizes
-extern int g_gemm_sms, g_gemm_skip_loads, g_gemm_spin_limit, g_gemm_prefetch;  // grouped_gemm.cu
+extern int g_gemm_sms, g_gemm_skip_loads, g_gemm_spin_limit, g_gemm_prefetch, g_gemm_tokens_as_n;  // grouped_gemm.cu
 
 struct TileCfg {
   int threads;
@@ -474,6 +474,9 @@ extern "C" int fmoe_tune(const char* key, int value) {
   } else if (k == "gemm_prefetch") {
     FMOE_REQUIRE(value >= 0 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: gemm_prefetch in [0, 64]");
     g_gemm_prefetch = value;
+  } else if (k == "gemm_tokens_as_n") {
+    FMOE_REQUIRE(value >= -1 && value <= 1, FMOE_ERR_ARG, "fmoe_tune: gemm_tokens_as_n is -1 (auto), 0 or 1");
+    g_gemm_tokens_as_n = value;
   } else if (k == "gemm_skip_loads") {
     g_gemm_skip_loads = value != 0;
   } else if (k == "gemm_spin_limit") {

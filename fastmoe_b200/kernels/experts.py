@@ -99,11 +99,6 @@ def _launch(a, w, offsets, counts, act, row_map=None, covers_all_rows=False, row
 class _GroupedGemm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, a, w, offsets, counts, act, row_map, covers_all_rows):
-        _check(a, w, offsets, counts)
-        if row_map is not None and (row_map.dtype != torch.int64 or row_map.numel() != a.shape[0]):
-            raise ValueError("row_map must be an int64 device tensor with one entry per row of a")
-        training = any(ctx.needs_input_grad[:2])
-        check_shapes(w.shape[1], w.shape[2], act, training)
         ctx.save_for_backward(a, w, offsets, counts, row_map)
         ctx.act, ctx.covers_all_rows = act, covers_all_rows
         return _launch(a, w, offsets, counts, act, row_map, covers_all_rows)
@@ -130,6 +125,18 @@ class _GroupedGemm(torch.autograd.Function):
         grad_a = _dgrad(grad_c, w, offsets, counts, ctx.covers_all_rows) if need_a else None
         grad_w = _wgrad(grad_c, a, w.shape, offsets, counts) if need_w else None
         return grad_a, grad_w, None, None, None, None, None
+
+
+def _apply(a, w, offsets, counts, act, row_map, covers_all_rows):
+    """Checks the arguments, then runs the product through autograd. Whether gradients will be
+    asked for is decided here, where the caller's grad mode is still visible: a width whose
+    gradients the kernels do not tile raises now rather than in the middle of a backward pass."""
+    _check(a, w, offsets, counts)
+    if row_map is not None and (row_map.dtype != torch.int64 or row_map.numel() != a.shape[0]):
+        raise ValueError("row_map must be an int64 device tensor with one entry per row of a")
+    training = torch.is_grad_enabled() and (a.requires_grad or w.requires_grad)
+    check_shapes(w.shape[1], w.shape[2], act, training)
+    return _GroupedGemm.apply(a, w, offsets, counts, act, row_map, covers_all_rows)
 
 
 def _dgrad(grad_c, w, offsets, counts, covers_all_rows=False, row_ptrs=None):
@@ -181,7 +188,7 @@ def grouped_gemm(a, w, offsets, counts, swiglu=False, row_map=None, covers_all_r
     saves the zero-fill of the output.
     """
     act = int(activation) if activation is not None else (ACT_SWIGLU if swiglu else ACT_NONE)
-    return _GroupedGemm.apply(a, w, offsets, counts, act, row_map, bool(covers_all_rows))
+    return _apply(a, w, offsets, counts, act, row_map, bool(covers_all_rows))
 
 
 def grouped_swiglu_ffn(x, w_gate_up, w_down, offsets, counts, row_map=None, covers_all_rows=False):

@@ -66,6 +66,9 @@ const char* fmoe_status_name(int status);
  * up to 256), "gather_ctas_per_sm" (-1 = auto, 0 = one CTA per work item,
  * else a persistent grid of 148 x value CTAs), "bwd_ctas_per_sm", "gemm_sms" (SMs the
  * grouped GEMM's persistent grid occupies, 1..148; fewer leaves room for NCCL kernels).
+ * "gemm_tokens_as_n" (which of fmoe_grouped_gemm's two forward kernels runs: 1 = the expert's
+ * tokens are the MMA's N dimension, in steps of 16 rows; 0 = they are its M dimension, in
+ * blocks of 128 rows; -1 = by the average rows per expert, the default),
  * "gemm_prefetch" (weight k-blocks of 64 the grouped GEMM asks into L2 ahead of its loads:
  * 0 = none, the default, since it measured slower; up to 64),
  * "host_chunks" (column slices of fmoe_combine_host's pipelined form: 1 = one slice, i.e.

@@ -12,6 +12,18 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=["tokens_as_m", "tokens_as_n"], autouse=True)
+def forward_kernel(request):
+    """Every test of this file runs with each of the two forward kernels behind fmoe_grouped_gemm:
+    tokens in 128-row blocks as the MMA's M dimension, and tokens in 16-row steps as its N
+    dimension (left to itself the library picks by the average rows per expert)."""
+    from fastmoe_b200 import _lib
+
+    _lib.tune("gemm_tokens_as_n", 1 if request.param == "tokens_as_n" else 0)
+    yield request.param
+    _lib.tune("gemm_tokens_as_n", -1)
+
+
 def _reference(a, w, counts, swiglu, gelu=False):
     out, o = [], 0
     for e, n in enumerate(counts):
@@ -47,6 +59,8 @@ CASES = [
     ([513, 127, 129], 1024, 1024, True),
     ([256, 257, 16, 17, 270, 0, 255], 256, 512, True),  # around the row-block boundaries
     ([256, 257, 16, 17, 270, 0, 255], 256, 512, False),
+    ([511, 513, 15, 31, 33, 1023, 1], 128, 256, False),  # equal shares of 2, 3 and 4 tiles; sub-box experts
+    ([511, 513, 15, 31, 33, 1023, 1], 128, 256, True),
 ]
 
 

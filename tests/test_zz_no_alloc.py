@@ -6,14 +6,18 @@ Checked through the C ABI against the regular pair fmoe_combine_plan +
 fmoe_combine_gather (caller-provided scratch) on two calls in a row with different
 inputs, so that anything left over from the first call would show in the second.
 Both paths run the same kernels in the same order: the outputs must be identical.
+The first call's output is also held against the CPU oracle's fp32 arithmetic on the
+same bf16 values, so the test stands on its own if the regular path were wrong too.
 
 This file sorts last on purpose: a run that stops at the first failure has then
 already run every other test.
 """
 
+import numpy as np
 import pytest
 import torch
 
+import oracle
 from fastmoe_b200 import _lib
 from fastmoe_b200.kernels import ops
 from fastmoe_b200.workloads import make_combine_workload
@@ -59,6 +63,10 @@ def test_static_entry_point_matches_regular_path_twice_in_a_row():
     a_static, a_ref = _both_paths(first, accumulate=0, out0=garbage)
     assert torch.equal(a_static, a_ref)
     assert float(a_ref.float().abs().max()) > 0 and not bool((a_ref == 7.0).all())
+    want = oracle.combine([e.float().cpu().numpy() for e in first.experts], first.indices.cpu().numpy(),
+                          first.weights.float().cpu().numpy(), first.T)  # fmt: skip
+    err = float(np.abs(a_static.float().cpu().numpy() - want).max()) / float(np.abs(want).max())
+    assert err <= 2e-2, err  # the bf16 bound of the other parity tests
     base = torch.randn(second.T, second.D, device=dev).to(torch.bfloat16)
     b_static, b_ref = _both_paths(second, accumulate=1, out0=base)
     assert torch.equal(b_static, b_ref)
