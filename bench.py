@@ -566,7 +566,7 @@ def run_ours(args, rank, world, local_rank):
 EP_WORKLOAD = "ep_moe_layer_cfg5_bf16_8192tok_D7168_E256_top8_swiglu2048"
 
 
-def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, mode="fused"):
+def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, mode="fused", expert_groups=None):
     """Expert-parallel MoE layer forward: 8192 tokens per rank, D=7168, 256 experts sharded
     evenly over the ranks, top-8 softmax router, SwiGLU experts 7168->2048->7168, weights
     N(0, 0.02). Micro-batches run on their own streams, the exchange of one overlapping the
@@ -614,7 +614,7 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, m
             try:
                 from fastmoe_b200.ep_fused import FusedExpertParallel
 
-                fused = FusedExpertParallel(moe, max_tokens=T)
+                fused = FusedExpertParallel(moe, max_tokens=T, expert_groups=expert_groups)
                 ep_mode = "fused peer stores"
             except Exception as exc:  # symmetric memory unavailable: every rank falls back alike
                 ep_mode = f"nccl all_to_all (fused path unavailable: {type(exc).__name__})"
@@ -791,7 +791,8 @@ def run_ep(args, rank, world, local_rank):
         from fastmoe_b200 import _lib
 
         _lib.tune("gemm_sms", args.gemm_sms)
-    r = ep_layer_bench(rank, world, local_rank, args.steps, args.warmup, args.micro_batches, args.ep_mode)
+    r = ep_layer_bench(rank, world, local_rank, args.steps, args.warmup, args.micro_batches, args.ep_mode,
+                       args.ep_groups)
     if rank != 0:
         return
     peak, kind = measured_tflops()
@@ -800,7 +801,8 @@ def run_ep(args, rank, world, local_rank):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": EP_WORKLOAD, **r["config"], "tokens_per_rank": r["tokens_per_rank"],
-                   "micro_batches": r["micro_batches"], "parallelism": f"ep{world}", "pass": "forward"},
+                   "micro_batches": r["micro_batches"], "expert_groups": r["expert_groups"],
+                   "parallelism": f"ep{world}", "pass": "forward"},
         "e2e": None, "gpu_launches": None,
         "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (share of the whole layer step)",
                      "achieved": r["gemm_tflops_per_gpu"], "peak": peak, "peak_kind": kind, "unit": "TFLOP/s",
@@ -1022,6 +1024,9 @@ def main():
     ap.add_argument("--ep-mode", choices=["fused", "nccl"], default="fused",
                     help="expert-parallel layer with several ranks: fused peer-store exchange or NCCL all-to-all")
     ap.add_argument("--gemm-sms", type=int, default=None, help="expert-parallel layer: SMs for the grouped GEMM")
+    ap.add_argument("--ep-groups", type=int, default=None,
+                    help="expert-parallel layer, fused exchange: groups the local experts are split into for the "
+                         "overlap of dispatch and GEMMs (default: 4 with several ranks)")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel layer part of the default run")
     ap.add_argument("--no-also", action="store_true", help="skip the skewed-combine and dispatch+combine sub-records")
     ap.add_argument("--cpu-port", action="store_true",

@@ -122,11 +122,15 @@ __global__ void __launch_bounds__(256) plan_finalize_kernel(const PlanArgs a) {
 // ---- all four steps in one cooperative launch -----------------------------------------
 // The separate kernels above are launch-latency bound (a few microseconds each for 64k
 // rows). This kernel runs the same steps with grid-wide barriers in between: zero the
-// histogram, count, scan (every CTA scans 512-wide pieces, then adds the prefix of the piece
-// totals, which it recomputes locally), place, finalize. The piece totals borrow the
-// row_of_slot section, which is not written before the last step.
+// histogram, count, scan inside 512-wide pieces (the piece-local offsets overwrite the
+// histogram), place, finalize. The prefix over the piece totals is not a step of its own:
+// every CTA works it out in shared memory at the start of the place step, which then adds
+// it on the fly and also writes the final offsets of the pieces the CTA owns. Every step
+// is a round trip of dependent global accesses plus a grid barrier, so one step fewer is
+// what counts. The piece totals borrow the row_of_slot section, which is not written before
+// the last step.
 constexpr int kFusedThreads = 512;
-constexpr int kFusedMaxPieces = 8192;  // pieces of 512 targets: T up to 4M
+constexpr int kFusedMaxPieces = 2048;  // pieces of 512 targets: T up to 1M (their prefix sits in shared memory)
 
 __device__ __forceinline__ int32_t block_exclusive_scan(int32_t v, int32_t* warp_sums, int32_t& total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -157,6 +161,7 @@ __global__ void __launch_bounds__(kFusedThreads) plan_fused_kernel(const PlanArg
   namespace cg = cooperative_groups;
   cg::grid_group grid = cg::this_grid();
   __shared__ int32_t warp_sums[32];
+  __shared__ int32_t piece_base[kFusedMaxPieces];
   const int64_t tid = blockIdx.x * static_cast<int64_t>(kFusedThreads) + threadIdx.x;
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * kFusedThreads;
   int32_t* piece_total = a.p.row_of_slot;
@@ -182,30 +187,37 @@ __global__ void __launch_bounds__(kFusedThreads) plan_fused_kernel(const PlanArg
     const int32_t v = t < a.T ? a.p.cnt[t] : 0;
     int32_t total;
     const int32_t excl = block_exclusive_scan(v, warp_sums, total);
-    if (t < a.T) a.p.seg_off[t] = excl;
+    if (t < a.T) a.p.cnt[t] = excl;  // the histogram has done its job: keep the piece-local offset in its place
     if (threadIdx.x == 0) piece_total[piece] = total;
   }
   grid.sync();
 
-  for (int64_t piece = blockIdx.x; piece < pieces; piece += gridDim.x) {
-    // prefix of the totals of all earlier pieces, summed by this CTA
-    int32_t part = 0;
-    for (int64_t q = threadIdx.x; q < piece; q += kFusedThreads) part += piece_total[q];
-    int32_t base;
-    block_exclusive_scan(part, warp_sums, base);
-    const int64_t t = piece * kFusedThreads + threadIdx.x;
-    if (t < a.T) a.p.seg_off[t] += base;
-    if (piece == pieces - 1 && threadIdx.x == 0) a.p.seg_off[a.T] = base + piece_total[piece];
+  {  // first row of every piece: exclusive prefix of the piece totals, by every CTA for itself
+    int32_t carry = 0;
+    for (int64_t q0 = 0; q0 < pieces; q0 += kFusedThreads) {
+      const int64_t q = q0 + threadIdx.x;
+      int32_t round_total;
+      const int32_t excl = block_exclusive_scan(q < pieces ? piece_total[q] : 0, warp_sums, round_total);
+      if (q < pieces) piece_base[q] = carry + excl;
+      carry += round_total;
+    }
+    __syncthreads();
+    for (int64_t piece = blockIdx.x; piece < pieces; piece += gridDim.x) {  // final offsets of my pieces
+      const int64_t t = piece * kFusedThreads + threadIdx.x;
+      if (t < a.T) a.p.seg_off[t] = a.p.cnt[t] + piece_base[piece];
+      if (piece == pieces - 1 && threadIdx.x == 0) a.p.seg_off[a.T] = carry;
+    }
   }
-  grid.sync();
-
   for (int64_t g = tid; g < a.N; g += nthreads) {
     const int32_t r = a.p.rank[g];
     if (r < 0) continue;
     const int64_t t = load_index(a.idx, g, a.idx_type);
-    a.p.seg_rows[a.p.seg_off[t] + r] = static_cast<int32_t>(g);
+    a.p.seg_rows[a.p.cnt[t] + piece_base[t / kFusedThreads] + r] = static_cast<int32_t>(g);
   }
   grid.sync();
+  // the last step: a kernel launched as a programmatic dependent of this one (the gather) may
+  // have its CTAs placed from here on; it still waits for this grid to complete before it reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   for (int64_t g = tid; g < a.N; g += nthreads) {
     int32_t r = a.p.rank[g];
@@ -236,6 +248,11 @@ __global__ void __launch_bounds__(kFusedThreads) plan_fused_kernel(const PlanArg
   }
   if (flags != 0 && a.status != nullptr) atomicOr(a.status, flags);
 }
+
+// fmoe_tune "plan_rows_per_thread": rows (or targets) each thread of the fused plan kernel
+// takes per step. The kernel is bound by the latency of its steps and of the grid barriers
+// between them, and a barrier over fewer CTAs is quicker, so a thread may well take several.
+int g_plan_rows_per_thread = 1;
 
 // Cooperative grid size for the current device (0 = cooperative launch not usable), cached.
 static int fused_grid_limit() {
@@ -307,7 +324,8 @@ extern "C" int fmoe_combine_plan(const int64_t* ptr_table, const int32_t* chunk_
   const int limit = N > 0 ? fused_grid_limit() : 0;
   if (limit > 0 && pieces <= N && pieces <= kFusedMaxPieces) {
     // one cooperative launch; the piece totals fit into the row_of_slot section (N ints)
-    const int64_t want = ((N > T ? N : T) + kFusedThreads - 1) / kFusedThreads;
+    const int64_t per_cta = static_cast<int64_t>(kFusedThreads) * (g_plan_rows_per_thread > 0 ? g_plan_rows_per_thread : 1);
+    const int64_t want = ((N > T ? N : T) + per_cta - 1) / per_cta;
     const int grid = static_cast<int>(want < limit ? want : limit);
     void* params[] = {&a};
     FMOE_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(plan_fused_kernel), dim3(grid),

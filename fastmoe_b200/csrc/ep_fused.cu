@@ -8,6 +8,12 @@
 
 namespace fmoe {
 
+// fmoe_tune "peer_ctas_per_sm": CTAs per SM of the dispatch kernel when it sends ONE group of
+// experts (a pass that is meant to run beside the persistent grouped GEMM): few, so that the
+// GEMM's CTA, which needs an SM's whole shared memory and a third of its registers, always
+// finds room beside them. A pass over all experts runs alone and uses one CTA per work item.
+int g_peer_ctas_per_sm = 2;
+
 struct PeerPermuteArgs {
   const void* x;
   int64_t x_row_stride;
@@ -273,6 +279,8 @@ extern "C" int fmoe_peer_barrier(const int64_t* flag_bases, int64_t world, int64
                "fmoe_peer_barrier: bad sizes (world %lld, rank %lld, timeout %lld ms)", (long long)world,
                (long long)rank, (long long)timeout_ms);
   FMOE_REQUIRE(flag_bases != nullptr, FMOE_ERR_ARG, "fmoe_peer_barrier: null pointer argument");
+  cudaFuncSetAttribute(peer_barrier_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);  // see fmoe_permute_peer_fwd
   peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       flag_bases, static_cast<int>(world), static_cast<int>(rank), seq,
       static_cast<unsigned long long>(timeout_ms) * 1000000ull, status);
@@ -377,14 +385,27 @@ extern "C" int fmoe_permute_peer_fwd(const void* x, int64_t x_row_stride, const 
     }
   a.tiles = static_cast<int>(best_tiles);
   const int64_t items = T * a.tiles;
-  const int grid = static_cast<int>(items < 0x7fffffffll ? items : 0x7fffffffll);
+  int64_t blocks = items < 0x7fffffffll ? items : 0x7fffffffll;
+  const bool one_group = local_lo > 0 || local_hi < experts_per_rank;
+  if (one_group && g_peer_ctas_per_sm > 0 && blocks > static_cast<int64_t>(kNumSMs) * g_peer_ctas_per_sm)
+    blocks = static_cast<int64_t>(kNumSMs) * g_peer_ctas_per_sm;  // the kernel strides over the items
+  const int grid = static_cast<int>(blocks);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int rc = 0;
+  // The kernel uses no shared memory, but it asks for the SM to be set up with the largest
+  // shared-memory share all the same: an SM cannot change that split while a CTA runs on it,
+  // so a grouped GEMM CTA (which needs nearly all of it) launched while this kernel is still
+  // running would otherwise wait for it to drain (measured: 200 us per step on 2 GPUs).
   FMOE_DISPATCH_DTYPE(dtype, DT, {
-    if (v == 1)
+    if (v == 1) {
+      cudaFuncSetAttribute(permute_peer_kernel<DT, 1>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared);
       permute_peer_kernel<DT, 1><<<grid, threads, 0, s>>>(a);
-    else
+    } else {
+      cudaFuncSetAttribute(permute_peer_kernel<DT, 2>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           cudaSharedmemCarveoutMaxShared);
       permute_peer_kernel<DT, 2><<<grid, threads, 0, s>>>(a);
+    }
     rc = check_launch("permute_peer_kernel");
   });
   return rc;

@@ -694,21 +694,30 @@ done:
   }
 }
 
-// ---- tokens as the MMA's N dimension ----------------------------------------------------------
-// The same product with the operands' roles exchanged: 128 WEIGHT rows are the MMA's M dimension
-// (the lanes of tensor memory) and an expert's TOKEN rows are its N dimension, which comes in
-// steps of 16 instead of blocks of 128. An expert with n <= 256 rows is ONE tile of round16(n)
-// tokens; a larger one is cut into ceil(n / 256) tiles of equal size (never a full tile plus a
-// sliver: a sliver would pull a whole weight tile through the SM for a fraction of the work).
-// With a few hundred rows per expert (256 experts on one GPU) this issues 3% more MMA work
-// than the rows need, where 128-row blocks issue 25% more. Operand bytes per MMA are the same
-// as in the kernel above. The accumulator arrives transposed (lane = output column, column =
-// token), so the epilogue turns 32-token chunks around through shared memory and stores whole
-// row segments. Tokens are loaded in 64-row boxes (up to four per stage, each issued by its own
-// lane of warp 0; rows past the tile's end ride along unused: the TMA unit's cost is per box,
-// and boxes of 16 rows measured 2x slower overall). For SwiGLU a tile holds 64 gate rows and
-// the 64 up rows of the same columns; the two factors of a column sit in different warps'
-// lanes of tensor memory and meet in shared memory on their way out.
+// ---- tokens as the MMA's N dimension, two weight tiles per token tile --------------------------
+// The same product with the operands' roles exchanged and a larger tile. WEIGHT rows are the
+// MMA's M dimension (the lanes of tensor memory) and an expert's TOKEN rows are its N dimension,
+// which comes in steps of 16 instead of blocks of 128: an expert with n <= 256 rows is ONE tile
+// of round16(n) tokens, a larger one is cut into ceil(n / 256) tiles of equal size (never a full
+// tile plus a sliver, which would pull whole weight tiles through the SM for a fraction of the
+// work). With a few hundred rows per expert this issues 3% more MMA work than the rows need,
+// where 128-row blocks issue 25% more.
+//
+// A tile pairs its tokens with TWO weight tiles of 128 rows, each MMA'd into its own 256-column
+// accumulator (all 512 columns of tensor memory): 64 KB of operands per k-block feed two
+// 128 x n x 64 products, where the kernel above moves 48 KB for one. Both kernels are bound by
+// what the TMA unit can bring into an SM, not by the tensor pipe (measured: time per k-block
+// grows with bytes and with the number of boxes, about 67 bytes per clock plus 50 clocks per
+// box), so operand bytes per MMA are what counts. The price is that the accumulators are not
+// double-buffered: a tile's epilogue and the next tile's first MMA do not overlap; the loads
+// do run ahead through the three pipeline stages meanwhile.
+//   plain / GELU   the two weight tiles are 256 consecutive output columns
+//   SwiGLU         128 gate rows and the 128 up rows of the same columns: a column's two
+//                  factors sit in the same lane of the two accumulators
+// The accumulator arrives transposed (lane = output column, column = token), so the epilogue
+// turns 32-token chunks around through shared memory and stores whole 256-byte row segments.
+// Tokens are loaded in 64-row boxes (up to four per stage, each issued by its own lane of warp
+// 0; rows past the tile's end ride along unused).
 struct TnArgs {
   const int64_t* offsets;
   const int64_t* counts;
@@ -717,7 +726,7 @@ struct TnArgs {
   __nv_bfloat16* C;
   int64_t ldc, R;
   int E;
-  int m_blocks;           // weight tiles per expert: N / 128, or ff / 64 for SwiGLU
+  int m_blocks;           // weight tile pairs per expert: N / 256, or ff / 128 for SwiGLU
   int k_blocks;           // K / 64
   int w_rows_per_expert;  // N (2 * ff for SwiGLU)
   int ff;                 // SwiGLU: row of the first "up" weight inside an expert
@@ -727,13 +736,14 @@ struct TnArgs {
   int32_t* status;
 };
 
-constexpr int kTnTokens = 256;                   // most tokens in one tile
-constexpr int kTnBox = 16;                       // step of a tile's token count (the MMA's N)
-constexpr int kTnLoadRows = 64;                  // token rows per TMA box
+constexpr int kTnTokens = 256;                       // most tokens in one tile
+constexpr int kTnBox = 16;                           // step of a tile's token count (the MMA's N)
+constexpr int kTnLoadRows = 64;                      // token rows per TMA box
 constexpr int kTnLoadBytes = kTnLoadRows * kBK * 2;  // 8 KB
-constexpr int kTnWBytes = 128 * kBK * 2;         // 16 KB of weights per stage
-constexpr int kTnTBytes = kTnTokens * kBK * 2;   // up to 32 KB of tokens per stage
-constexpr int kTnEpiBytes = 24576;  // epilogue: [2][32][128] bf16 out, or for SwiGLU [2][32][64] bf16 out + [2][32][64] fp32 up
+constexpr int kTnWBytes = 2 * 128 * kBK * 2;         // 32 KB: two weight tiles per stage
+constexpr int kTnTBytes = kTnTokens * kBK * 2;       // up to 32 KB of tokens per stage
+constexpr int kTnStages = 3;
+static_assert(kTnStages * (kTnWBytes + kTnTBytes) == kStages * kStageBytes, "same pipeline memory as grouped_gemm_kernel");
 
 struct TnTile {
   int expert, mb, rows, n;  // rows = valid tokens, n = rows rounded up to 16 (the MMA's N)
@@ -755,7 +765,7 @@ __device__ __forceinline__ TnTile tn_locate(int tile, const int* split_prefix, c
   c.mb = local / splits;
   const int sp = local - c.mb * splits;
   const int64_t n = expert_rows(a.offsets, a.counts, a.R, lo);
-  const int64_t per = ((n + splits - 1) / splits + kTnBox - 1) / kTnBox * kTnBox;  // equal shares, in whole boxes
+  const int64_t per = ((n + splits - 1) / splits + kTnBox - 1) / kTnBox * kTnBox;  // equal shares, in steps of 16
   const int64_t begin = sp * per;
   int64_t rows = n - begin;
   rows = rows < 0 ? 0 : (rows < per ? rows : per);
@@ -782,11 +792,11 @@ __device__ __forceinline__ bool epi_all(bool ok) {
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
     grouped_gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                           const TnArgs a) {  // map_a: box 64 x 64 token rows; map_w: box 64 x 128 (64 x 64 for SwiGLU)
+                           const TnArgs a) {  // map_a: box 64 x 64 token rows; map_w: box 64 x 128 weight rows
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_w = smem;
-  uint8_t* smem_t = smem + kStages * kTnWBytes;
+  uint8_t* smem_t = smem + kTnStages * kTnWBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
   uint64_t* empty = full + kStages;
   uint64_t* tmem_full = empty + kStages;
@@ -795,8 +805,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   int* abort_flag = reinterpret_cast<int*>(tmem_base_slot + 1);
   uint64_t* drain = reinterpret_cast<uint64_t*>(abort_flag + 1);
   __nv_bfloat16* turn = reinterpret_cast<__nv_bfloat16*>(smem + kStages * kStageBytes + 256);  // [2][32 tokens][128 cols]
-  float* up_buf = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256 + 8192);  // SwiGLU: [2][32 tokens][64 cols]
-  int* split_prefix = reinterpret_cast<int*>(smem + kStages * kStageBytes + 256 + kTnEpiBytes);  // [E + 1]
+  int* split_prefix = reinterpret_cast<int*>(smem + kStages * kStageBytes + 256 + kEpiStageBytes);  // [E + 1]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int fills = 0;
@@ -811,14 +820,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (threadIdx.x == 0) {
     split_prefix[0] = 0;
     *abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kTnStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], 4);
-    }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_empty[0], 4);
     mbar_init(drain, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -849,13 +856,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int total_tiles = split_prefix[a.E] * a.m_blocks;
 
   if (warp == 0) {
-    // ---- TMA producer: lane 0 waits and announces the bytes, every lane issues its boxes ------
+    // ---- TMA producer: lane 0 waits and announces the bytes, six lanes issue one box each ------
     int stage = 0;
     uint32_t phase = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !a.skip_loads; tile += gridDim.x) {
       const TnTile c = tn_locate(tile, split_prefix, a);
       const int boxes = (c.n + kTnLoadRows - 1) / kTnLoadRows;
       const int w_row = c.expert * a.w_rows_per_expert;
+      // lane 0: first weight tile, lane 1: second one (the next 128 output columns, or the up rows)
+      const int my_w_row = a.swiglu ? w_row + (lane ? a.ff : 0) + c.mb * 128 : w_row + c.mb * 256 + lane * 128;
       for (int kb = 0; kb < a.k_blocks; ++kb) {
         int ok = 1;
         if (lane == 0) ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, a.spin_limit) ? 1 : 0;
@@ -866,21 +875,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           ++fills;
         }
         __syncwarp();
-        if (a.swiglu) {
-          if (lane < 2)  // 64 gate rows (lanes 0-63 of tensor memory), then the 64 up rows of the same columns
-            tma_load_2d(smem_w + stage * kTnWBytes + lane * (kTnWBytes / 2), &map_w, kb * kBK,
-                        w_row + (lane ? a.ff : 0) + c.mb * 64, &full[stage]);
-        } else if (lane == 0) {
-          tma_load_2d(smem_w + stage * kTnWBytes, &map_w, kb * kBK, w_row + c.mb * 128, &full[stage]);
-        }
+        if (lane < 2)
+          tma_load_2d(smem_w + stage * kTnWBytes + lane * (kTnWBytes / 2), &map_w, kb * kBK, my_w_row, &full[stage]);
         if (lane >= 8 && lane - 8 < boxes)
           tma_load_2d(smem_t + stage * kTnTBytes + (lane - 8) * kTnLoadBytes, &map_a, kb * kBK,
                       static_cast<int>(c.row0) + (lane - 8) * kTnLoadRows, &full[stage]);
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (++stage == kTnStages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1 && lane == 0) {
-    // ---- MMA issuer ---------------------------------------------------------------------------
+    // ---- MMA issuer: two products per k-step, one per weight tile, the tokens shared -----------
     int stage = 0;
     uint32_t phase = 0;
     int it = 0;
@@ -889,91 +893,90 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // D fp32, A and B bf16, both K-major, M = 128 weight rows, N = this tile's tokens
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(c.n >> 3) << 17) |
                              (static_cast<uint32_t>(128 >> 4) << 24);
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, a.spin_limit)) goto timed_out;
+      if (!mbar_wait(&tmem_empty[0], (it & 1) ^ 1, abort_flag, a.spin_limit)) goto timed_out;
       tcgen05_fence_after();
-      const uint32_t tmem_d = tmem_base + acc * kTnTokens;
       for (int kb = 0; kb < a.k_blocks; ++kb) {
         if (!mbar_wait(&full[stage], phase, abort_flag, a.spin_limit)) goto timed_out;
         tcgen05_fence_after();
         mma_issued = true;
-        const uint64_t dw = smem_desc(smem_u32(smem_w + stage * kTnWBytes));
+        const uint64_t dw0 = smem_desc(smem_u32(smem_w + stage * kTnWBytes));
+        const uint64_t dw1 = smem_desc(smem_u32(smem_w + stage * kTnWBytes + kTnWBytes / 2));
         const uint64_t dt = smem_desc(smem_u32(smem_t + stage * kTnTBytes));
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) umma_bf16(tmem_d, dw + 2 * k, dt + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          umma_bf16(tmem_base, dw0 + 2 * k, dt + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_bf16(tmem_base + kTnTokens, dw1 + 2 * k, dt + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
         umma_commit(&empty[stage]);
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (++stage == kTnStages) { stage = 0; phase ^= 1; }
       }
-      umma_commit(&tmem_full[acc]);
+      umma_commit(&tmem_full[0]);
     }
   } else if (warp >= 2) {
     // ---- epilogue: lane = output column, TMEM column = token -----------------------------------
     const int quarter = warp & 3;
-    const int tid = threadIdx.x - 64;                  // 0..127 among the epilogue threads
-    const int out_cols = a.swiglu ? 64 : 128;          // output columns of one tile
-    const int pieces = out_cols / 8;                   // 16-byte pieces per token row
+    const int tid = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    const int halves = a.swiglu ? 1 : 2;  // passes over the tile: one per 128 output columns
     int it = 0;
     uint32_t chunk = 0;  // running count of 32-token chunks: its parity picks the turning buffer
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
       const TnTile c = tn_locate(tile, split_prefix, a);
-      const bool got = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, a.spin_limit);
+      const bool got = mbar_wait(&tmem_full[0], it & 1, abort_flag, a.spin_limit);
       if (!epi_all(got)) goto timed_out;  // the four warps go on, or give up, together
       tcgen05_fence_after();
-      const uint32_t taddr = tmem_base + acc * kTnTokens + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int64_t col0 = static_cast<int64_t>(c.mb) * (a.swiglu ? 128 : 256);
 #pragma unroll 1
-      for (int c0 = 0; c0 < c.n; c0 += 32, ++chunk) {
-        __nv_bfloat16* buf = turn + (chunk & 1) * (32 * 128);
-        uint32_t r[32];
-        tmem_ld32(taddr + c0, r);
-        tmem_ld_wait();
-        if (a.swiglu) {
-          // quarters 2 and 3 hold the up factors of the columns whose gate factors quarters 0 and 1 hold
-          float* ups = up_buf + (chunk & 1) * (32 * 64);
-          if (quarter >= 2) {
+      for (int half = 0; half < halves; ++half) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < c.n; c0 += 32, ++chunk) {
+          __nv_bfloat16* buf = turn + (chunk & 1) * (32 * 128);
+          uint32_t r[32];
+          if (a.swiglu) {
+            uint32_t u[32];
+            tmem_ld32(taddr + c0, r);
+            tmem_ld32(taddr + kTnTokens + c0, u);
+            tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) ups[j * 64 + (quarter - 2) * 32 + lane] = __uint_as_float(r[j]);
-          }
-          epi_bar_sync();
-          if (quarter < 2) {
+            for (int j = 0; j < 32; ++j)
+              buf[j * 128 + quarter * 32 + lane] =
+                  __float2bfloat16_rn(silu(__uint_as_float(r[j])) * __uint_as_float(u[j]));
+          } else {
+            tmem_ld32(taddr + half * kTnTokens + c0, r);
+            tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int at = j * 64 + quarter * 32 + lane;
-              buf[at] = __float2bfloat16_rn(silu(__uint_as_float(r[j])) * ups[at]);
+              const float v = __uint_as_float(r[j]);
+              buf[j * 128 + quarter * 32 + lane] = __float2bfloat16_rn(a.gelu ? gelu_erf(v) : v);
             }
           }
-        } else {
+          if (half == halves - 1 && c0 + 32 >= c.n) {
+            // the last read of tensor memory for this tile: the next tile's MMAs may start
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[0]);
+          }
+          epi_bar_sync();  // the chunk is complete in shared memory (the other buffer is refilled next)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float v = __uint_as_float(r[j]);
-            buf[j * 128 + quarter * 32 + lane] = __float2bfloat16_rn(a.gelu ? gelu_erf(v) : v);
-          }
-        }
-        epi_bar_sync();  // the chunk is complete in shared memory (the other buffer is being refilled next)
-        const int rows_per_pass = 128 / pieces;
-        for (int r0 = 0; r0 < 32; r0 += rows_per_pass) {
-          const int tr = r0 + tid / pieces, q = tid % pieces;
-          const int token = c0 + tr;
-          const int64_t a_row = c.row0 + token;
-          if (token < c.rows && a_row < a.R) {
-            char* row = nullptr;
-            if (a.c_row_ptrs != nullptr) row = reinterpret_cast<char*>(a.c_row_ptrs[a_row]);
-            if (row == nullptr && a.C != nullptr) {
-              const int64_t out_row = (a.c_row_ptrs == nullptr && a.c_row_map != nullptr) ? a.c_row_map[a_row] : a_row;
-              row = reinterpret_cast<char*>(a.C + out_row * a.ldc);
-            }
-            if (row != nullptr) {
-              const uint4 val = *reinterpret_cast<const uint4*>(buf + tr * out_cols + q * 8);
-              *reinterpret_cast<uint4*>(row + (static_cast<int64_t>(c.mb) * out_cols + q * 8) * 2) = val;
+          for (int r0 = 0; r0 < 32; r0 += 8) {  // 8 token rows per pass, 16 threads x 16 bytes per row
+            const int tr = r0 + (tid >> 4), q = tid & 15;
+            const int token = c0 + tr;
+            const int64_t a_row = c.row0 + token;
+            if (token < c.rows && a_row < a.R) {
+              char* row = nullptr;
+              if (a.c_row_ptrs != nullptr) row = reinterpret_cast<char*>(a.c_row_ptrs[a_row]);
+              if (row == nullptr && a.C != nullptr) {
+                const int64_t out_row = (a.c_row_ptrs == nullptr && a.c_row_map != nullptr) ? a.c_row_map[a_row] : a_row;
+                row = reinterpret_cast<char*>(a.C + out_row * a.ldc);
+              }
+              if (row != nullptr) {
+                const uint4 val = *reinterpret_cast<const uint4*>(buf + tr * 128 + q * 8);
+                *reinterpret_cast<uint4*>(row + (col0 + half * 128 + q * 8) * 2) = val;
+              }
             }
           }
         }
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
   }
   goto done;
@@ -983,7 +986,7 @@ timed_out:
   if (a.status != nullptr) atomicOr(a.status, FMOE_STATUS_WAIT_TIMEOUT);
 
 done:
-  drain_on_exit(warp, lane, fills, mma_issued, full, drain, abort_flag, kStages, a.spin_limit);
+  drain_on_exit(warp, lane, fills, mma_issued, full, drain, abort_flag, kTnStages, a.spin_limit);
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -1085,7 +1088,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
     CUtensorMap map_t, map_wt;
     int rc_t = make_map(&map_t, a, R, K, "A (64-row boxes)", kTnLoadRows);
     if (rc_t != 0) return rc_t;
-    rc_t = make_map(&map_wt, w, E * N, K, "W", swiglu ? 64 : 128);
+    rc_t = make_map(&map_wt, w, E * N, K, "W", 128);
     if (rc_t != 0) return rc_t;
     TnArgs t;
     t.offsets = offsets;
@@ -1096,7 +1099,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
     t.ldc = swiglu ? N / 2 : N;
     t.R = R;
     t.E = static_cast<int>(E);
-    t.m_blocks = static_cast<int>(swiglu ? (N / 2) / 64 : N / 128);
+    t.m_blocks = static_cast<int>(swiglu ? (N / 2) / 128 : N / 256);
     t.k_blocks = static_cast<int>(K / kBK);
     t.w_rows_per_expert = static_cast<int>(N);
     t.ff = static_cast<int>(N / 2);
@@ -1105,9 +1108,9 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
     t.skip_loads = g_gemm_skip_loads;
     t.spin_limit = static_cast<uint32_t>(g_gemm_spin_limit);
     t.status = status;
-    const size_t smem_t = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + kTnEpiBytes + sizeof(int) * (E + 2);
+    const size_t smem_t = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256 + kEpiStageBytes + sizeof(int) * (E + 2);
     FMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   1024 + kStages * kStageBytes + 256 + kTnEpiBytes +
+                                   1024 + kStages * kStageBytes + 256 + kEpiStageBytes +
                                        static_cast<int>(sizeof(int)) * (kMaxExperts + 2)));
     // upper bound of the tile count, known without reading the counts: one partial tile per expert
     const int64_t max_tiles_t = (R / kTnTokens + E) * t.m_blocks;

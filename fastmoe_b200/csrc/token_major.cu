@@ -20,8 +20,11 @@ static int g_gather_v = 0;         // vectors per thread, 0 = choose from D
 static int g_gather_threads = 0;   // threads per CTA, 0 = choose from D
 static int g_gather_ctas_per_sm = -1;  // persistent grid = 148 * this; 0 = one CTA per item; -1 = auto
 static int g_bwd_ctas_per_sm = 3;
+static int g_gather_pdl = 1;  // launch the gather kernels as programmatic dependents of their predecessor
 int g_host_chunks = 1;  // column slices of fmoe_combine_host (host_api.cu); 0 = choose from the sizes
 extern int g_gemm_sms, g_gemm_skip_loads, g_gemm_spin_limit, g_gemm_prefetch, g_gemm_tokens_as_n;  // grouped_gemm.cu
+extern int g_peer_ctas_per_sm;  // ep_fused.cu
+extern int g_plan_rows_per_thread;  // combine_plan.cu
 
 struct TileCfg {
   int threads;
@@ -153,6 +156,10 @@ __global__ void __launch_bounds__(256)
   using Ty = typename El::type;
   constexpr int U = 4;  // rows in flight
   const int64_t items = T * tiles;
+  // Launched as a programmatic dependent of the kernel that writes what `src` reads (the plan
+  // build), this kernel's CTAs may already be resident while that kernel finishes: wait for
+  // it here. Without such a launch the instruction returns at once.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int64_t item = blockIdx.x; item < items; item += gridDim.x) {
     const int64_t t = item / tiles;
     const int tile = static_cast<int>(item - t * tiles);
@@ -275,7 +282,20 @@ static int launch_gather_sum(const Source& src, void* out, int64_t out_row_strid
       ctas = slot;
     }
     const int g = static_cast<int>(clamp_grid(T * cfg.tiles, ctas));
-    kernel<<<g, cfg.threads, 0, s>>>(src, out, out_row_stride, T, dvec, cfg.tiles, accumulate);
+    // programmatic dependent launch: the CTAs may be placed while the previous kernel of the
+    // stream drains (they wait inside, see the kernel); saves the launch gap after the plan build
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(g);
+    lc.blockDim = dim3(cfg.threads);
+    lc.dynamicSmemBytes = 0;
+    lc.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_gather_pdl ? 1 : 0;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    int acc = accumulate;
+    cudaLaunchKernelEx(&lc, kernel, src, out, out_row_stride, T, dvec, cfg.tiles, acc);
   };
   switch (cfg.v) {
     case 1: launch(gather_sum_kernel<DT, 1, WEIGHTED, Source>); break;
@@ -477,6 +497,14 @@ extern "C" int fmoe_tune(const char* key, int value) {
   } else if (k == "gemm_tokens_as_n") {
     FMOE_REQUIRE(value >= -1 && value <= 1, FMOE_ERR_ARG, "fmoe_tune: gemm_tokens_as_n is -1 (auto), 0 or 1");
     g_gemm_tokens_as_n = value;
+  } else if (k == "gather_pdl") {
+    g_gather_pdl = value != 0;
+  } else if (k == "plan_rows_per_thread") {
+    FMOE_REQUIRE(value >= 1 && value <= 64, FMOE_ERR_ARG, "fmoe_tune: plan_rows_per_thread in [1, 64]");
+    g_plan_rows_per_thread = value;
+  } else if (k == "peer_ctas_per_sm") {
+    FMOE_REQUIRE(value >= 0 && value <= 16, FMOE_ERR_ARG, "fmoe_tune: peer_ctas_per_sm in [0, 16]");
+    g_peer_ctas_per_sm = value;
   } else if (k == "gemm_skip_loads") {
     g_gemm_skip_loads = value != 0;
   } else if (k == "gemm_spin_limit") {

@@ -113,7 +113,10 @@ class FusedExpertParallel:
         flag_bases = self._peer_addresses(h_flags, self._flags)
         self._flag_bases = (flag_bases, flag_bases + 32 * 4)
         self._seq = [0, 0]
+        # group overlap: dispatches on a side stream, the GEMMs on a stream of higher priority, so
+        # that the GEMM's CTAs are placed first and the copy kernel's fill what is left of the SMs
         self._side = torch.cuda.Stream(device=self.device)
+        self._gemm_stream = torch.cuda.Stream(device=self.device, priority=-1)
         self._grad = None
         torch.cuda.synchronize(self.device)  # the flags are zero before anybody's first barrier
         dist.barrier(self.group)
@@ -220,17 +223,22 @@ class FusedExpertParallel:
             self._barrier()  # all rows for my experts have landed
             run_experts(0, el)
         else:
-            main, side, eg = torch.cuda.current_stream(self.device), self._side, el // G
+            main, side, hi, eg = torch.cuda.current_stream(self.device), self._side, self._gemm_stream, el // G
             side.wait_stream(main)
+            hi.wait_stream(main)
             arrived = []
             with torch.cuda.stream(side):
                 for g in range(G):
                     send(g * eg, (g + 1) * eg)
                     self._barrier(1)  # group g's rows have landed on every rank
                     arrived.append(side.record_event())
-            for g in range(G):
-                main.wait_event(arrived[g])
-                run_experts(g * eg, (g + 1) * eg)
+            with torch.cuda.stream(hi):
+                for g in range(G):
+                    hi.wait_event(arrived[g])
+                    run_experts(g * eg, (g + 1) * eg)
+                self._barrier()  # every expert output for my tokens has landed
+            main.wait_stream(hi)
+            return hidden
         self._barrier()  # every expert output for my tokens has landed
         return hidden
 

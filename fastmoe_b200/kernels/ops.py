@@ -260,7 +260,7 @@ def build_combine_plan(expert_tensors, indices, weights, n_out, metadata=None) -
     # one cooperative launch when the piece totals of the scan fit (see csrc/combine_plan.cu)
     pieces = (n_out + 511) // 512
     _call(
-        "fmoe_combine_plan", 1 if 0 < pieces <= min(n_rows, 8192) else 4,
+        "fmoe_combine_plan", 1 if 0 < pieces <= min(n_rows, 2048) else 4,
         ptr_table.data_ptr(), chunk_sizes.data_ptr(), expert_offsets.data_ptr(),
         indices.data_ptr(), _ITYPES[indices.dtype], weights.data_ptr(), _DTYPES[weights.dtype],
         num_experts, n_rows, n_out, dim, _DTYPES[dtype],

@@ -69,6 +69,8 @@ const char* fmoe_status_name(int status);
  * "gemm_tokens_as_n" (which of fmoe_grouped_gemm's two forward kernels runs: 1 = the expert's
  * tokens are the MMA's N dimension, in steps of 16 rows; 0 = they are its M dimension, in
  * blocks of 128 rows; -1 = by the average rows per expert, the default),
+ * "peer_ctas_per_sm" (CTAs per SM of fmoe_permute_peer_fwd when it sends one group of experts
+ * beside a running grouped GEMM: default 2; 0 = one CTA per work item, as for a pass over all),
  * "gemm_prefetch" (weight k-blocks of 64 the grouped GEMM asks into L2 ahead of its loads:
  * 0 = none, the default, since it measured slower; up to 64),
  * "host_chunks" (column slices of fmoe_combine_host's pipelined form: 1 = one slice, i.e.
