@@ -425,6 +425,7 @@ def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
 
     from fastmoe_b200 import _lib
+    from fastmoe_b200.kernels import ops
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the product has no CPU path")
@@ -473,7 +474,11 @@ def run_ours(args, rank, world, local_rank):
         e2e_step()  # returns after its stream has drained
     barrier()
     e2e_s = time.perf_counter() - t0
-    assert torch.equal(out_host.to(device), out), "host-buffer call and device call disagree"
+    if ops.combine_mode() == "gather":  # the same kernels in the same order: identical bits
+        assert torch.equal(out_host.to(device), out), "host-buffer call and device call disagree"
+    else:  # the scatter form adds in bf16, in arrival order: equal within the bf16 bound only
+        ref = out_host.to(device).float()
+        assert float((out.float() - ref).abs().max() / ref.abs().max()) <= 2e-2
 
     # ---- aggregate over ranks -------------------------------------------------------
     stats = torch.tensor([elapsed_ms, e2e_s], dtype=torch.float64, device=device)

@@ -285,6 +285,7 @@ extern "C" int fmoe_combine_plan(const int64_t* ptr_table, const int32_t* chunk_
                                  const void* w, int w_dtype, int64_t E, int64_t N, int64_t T,
                                  int64_t D, int dtype, void* plan, size_t plan_bytes,
                                  int32_t* status, void* stream) {
+  FMOE_RANGE("fmoe_combine_plan");
   using namespace fmoe;
   FMOE_REQUIRE(valid_dtype(dtype) && valid_dtype(w_dtype), FMOE_ERR_ARG,
                "fmoe_combine_plan: bad dtype %d / w_dtype %d", dtype, w_dtype);

@@ -212,6 +212,7 @@ extern "C" int fmoe_combine_scatter(const int64_t* ptr_table, const int32_t* chu
                                     const void* w, int w_dtype, void* out, int64_t out_row_stride,
                                     int64_t E, int64_t N, int64_t T, int64_t D, int dtype,
                                     int32_t* status, void* stream) {
+  FMOE_RANGE("fmoe_combine_scatter");
   using namespace fmoe;
   FMOE_REQUIRE(valid_dtype(dtype) && valid_dtype(w_dtype), FMOE_ERR_ARG,
                "fmoe_combine_scatter: bad dtype %d / w_dtype %d", dtype, w_dtype);

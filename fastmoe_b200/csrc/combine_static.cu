@@ -49,6 +49,7 @@ extern "C" int fmoe_combine_fwd_static(const int64_t* ptr_table, const int32_t* 
                                        int64_t out_row_stride, int64_t E, int64_t N, int64_t T,
                                        int64_t D, int dtype, int accumulate, int32_t* status,
                                        void* stream) {
+  FMOE_RANGE("fmoe_combine_fwd_static");
   using namespace fmoe;
   FMOE_REQUIRE(N >= 0 && T >= 0, FMOE_ERR_ARG, "fmoe_combine_fwd_static: negative size");
   const size_t need = fmoe_combine_plan_bytes(N, T);

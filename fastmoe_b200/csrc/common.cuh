@@ -9,6 +9,8 @@
 #include <cstdarg>
 #include <cstdio>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/fastmoe_b200.h"
 
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
@@ -36,6 +38,17 @@ int check_cuda(cudaError_t e, const char* what);
   } while (0)
 
 inline int check_launch(const char* kernel) { return check_cuda(cudaGetLastError(), kernel); }
+
+// NVTX range around the host side of an entry point (header-only NVTX 3: a no-op unless a
+// profiler has injected its library): timelines show which call enqueued which kernels, as
+// the reference marks its pipeline stages (src/fastmoe/models/tiny_model.py:527-622).
+struct ScopedRange {
+  explicit ScopedRange(const char* name) { nvtxRangePushA(name); }
+  ~ScopedRange() { nvtxRangePop(); }
+  ScopedRange(const ScopedRange&) = delete;
+  ScopedRange& operator=(const ScopedRange&) = delete;
+};
+#define FMOE_RANGE(name) ::fmoe::ScopedRange fmoe_range_(name)
 
 inline bool valid_dtype(int dt) { return dt == FMOE_F32 || dt == FMOE_BF16 || dt == FMOE_F16; }
 inline bool valid_itype(int it) { return it == FMOE_I64 || it == FMOE_I32; }

@@ -275,6 +275,7 @@ using namespace fmoe;
 
 extern "C" int fmoe_peer_barrier(const int64_t* flag_bases, int64_t world, int64_t rank, int32_t seq,
                                  int64_t timeout_ms, int32_t* status, void* stream) {
+  FMOE_RANGE("fmoe_peer_barrier");
   FMOE_REQUIRE(world > 0 && world <= 32 && rank >= 0 && rank < world && timeout_ms > 0, FMOE_ERR_ARG,
                "fmoe_peer_barrier: bad sizes (world %lld, rank %lld, timeout %lld ms)", (long long)world,
                (long long)rank, (long long)timeout_ms);
@@ -292,6 +293,7 @@ extern "C" int fmoe_ep_layout(const int64_t* counts_all, int64_t world, int64_t 
                               int64_t* dst_row0, int64_t* counts_local, int64_t* offsets_local, int64_t* rows_used,
                               int64_t* row_ptrs, int64_t* grad_row_ptrs, int64_t* scratch, int32_t* status,
                               void* stream) {
+  FMOE_RANGE("fmoe_ep_layout");
   FMOE_REQUIRE(world > 0 && E > 0 && rank >= 0 && rank < world && cap_rows >= 0 && row_bytes > 0, FMOE_ERR_ARG,
                "fmoe_ep_layout: bad sizes");
   FMOE_REQUIRE(E % world == 0, FMOE_ERR_ARG, "fmoe_ep_layout: E=%lld is not a multiple of world=%lld", (long long)E,
@@ -333,6 +335,7 @@ extern "C" int fmoe_permute_peer_fwd(const void* x, int64_t x_row_stride, const 
                                      int64_t K, int64_t D, int64_t E, int64_t experts_per_rank,
                                      int64_t cap_rows, void* ret_local, int64_t local_lo, int64_t local_hi,
                                      int dtype, int32_t* status, void* stream) {
+  FMOE_RANGE("fmoe_permute_peer_fwd");
   FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_permute_peer_fwd: bad dtype %d", dtype);
   FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0 && E > 0 && experts_per_rank > 0 && cap_rows >= 0, FMOE_ERR_ARG,
                "fmoe_permute_peer_fwd: bad sizes");

@@ -1062,6 +1062,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
                                  const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
                                  int64_t E, int64_t R, int64_t N, int64_t K, int activation, int32_t* status,
                                  void* stream) {
+  FMOE_RANGE("fmoe_grouped_gemm");
   FMOE_REQUIRE(activation >= FMOE_ACT_NONE && activation <= FMOE_ACT_GELU, FMOE_ERR_ARG,
                "fmoe_grouped_gemm: activation must be FMOE_ACT_NONE, FMOE_ACT_SWIGLU or FMOE_ACT_GELU");
   const int swiglu = activation == FMOE_ACT_SWIGLU;
@@ -1160,6 +1161,7 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
 extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* grad_a, const int64_t* offsets,
                                        const int64_t* counts, const int64_t* row_ptrs, int64_t E, int64_t R,
                                        int64_t N, int64_t K, int32_t* status, void* stream) {
+  FMOE_RANGE("fmoe_grouped_gemm_dgrad");
   FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm_dgrad: bad sizes");
   FMOE_REQUIRE(E <= kMaxExperts, FMOE_ERR_UNSUPPORTED, "fmoe_grouped_gemm_dgrad: supports E <= %d", kMaxExperts);
   FMOE_REQUIRE(N % kBK == 0 && K % kBN == 0, FMOE_ERR_UNSUPPORTED,
@@ -1210,6 +1212,7 @@ extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* 
 extern "C" int fmoe_grouped_gemm_wgrad(const void* grad_c, const void* a, void* grad_w, const int64_t* offsets,
                                        const int64_t* counts, int64_t E, int64_t R, int64_t N, int64_t K,
                                        int32_t* status, void* stream) {
+  FMOE_RANGE("fmoe_grouped_gemm_wgrad");
   FMOE_REQUIRE(E >= 0 && R >= 0 && N > 0 && K > 0, FMOE_ERR_ARG, "fmoe_grouped_gemm_wgrad: bad sizes");
   FMOE_REQUIRE(N % kBM == 0 && K % kBN == 0, FMOE_ERR_UNSUPPORTED,
                "fmoe_grouped_gemm_wgrad: N=%lld must be a multiple of %d and K=%lld of %d", (long long)N, kBM,

@@ -122,6 +122,7 @@ extern "C" int fmoe_combine_host(const void* const* expert_rows_host,
                                  int idx_type, const void* w_host, int w_dtype, void* out_host,
                                  int64_t E, int64_t N, int64_t T, int64_t D, int dtype, void* arena,
                                  size_t arena_bytes, void* stream) {
+  FMOE_RANGE("fmoe_combine_host");
   FMOE_REQUIRE(valid_dtype(dtype) && valid_dtype(w_dtype) && valid_itype(idx_type), FMOE_ERR_ARG,
                "fmoe_combine_host: bad dtype/w_dtype/idx_type");
   FMOE_REQUIRE(E >= 0 && N >= 0 && T >= 0 && D >= 0, FMOE_ERR_ARG,

@@ -239,6 +239,7 @@ using namespace fmoe;
 
 extern "C" int fmoe_route_topk(const void* logits, int dtype, int64_t T, int64_t E, int64_t K,
                                int64_t* topk_idx, void* topk_w, int w_dtype, void* stream) {
+  FMOE_RANGE("fmoe_route_topk");
   FMOE_REQUIRE(valid_dtype(dtype) && valid_dtype(w_dtype), FMOE_ERR_ARG,
                "fmoe_route_topk: bad dtype %d / w_dtype %d", dtype, w_dtype);
   FMOE_REQUIRE(T >= 0 && E >= 0 && K >= 0, FMOE_ERR_ARG, "fmoe_route_topk: negative size");
@@ -283,6 +284,7 @@ extern "C" int fmoe_build_index(const int64_t* topk_idx, const void* topk_w, int
                                 void* sorted_w, int64_t* counts, int64_t* offsets,
                                 int64_t* rank_counts, int32_t* slot_of, void* scratch,
                                 size_t scratch_bytes, int32_t* status, void* stream) {
+  FMOE_RANGE("fmoe_build_index");
   FMOE_REQUIRE(valid_dtype(w_dtype), FMOE_ERR_ARG, "fmoe_build_index: bad w_dtype %d", w_dtype);
   FMOE_REQUIRE(T >= 0 && E > 0 && K >= 0 && world > 0, FMOE_ERR_ARG,
                "fmoe_build_index: sizes must be T >= 0, E > 0, K >= 0, world > 0");

@@ -518,6 +518,7 @@ extern "C" int fmoe_tune(const char* key, int value) {
 
 extern "C" int fmoe_combine_gather(const void* plan, void* out, int64_t out_row_stride, int64_t N,
                                    int64_t T, int64_t D, int dtype, int accumulate, void* stream) {
+  FMOE_RANGE("fmoe_combine_gather");
   FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_combine_gather: bad dtype %d", dtype);
   FMOE_REQUIRE(N >= 0 && T >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_combine_gather: negative size");
   FMOE_REQUIRE(N < (1ll << 31) && T < (1ll << 31) - 1, FMOE_ERR_UNSUPPORTED,
@@ -558,6 +559,7 @@ int combine_gather_window(const void* plan, void* out, int64_t out_row_stride, i
 extern "C" int fmoe_combine_bwd(const void* plan, const void* grad_out, int64_t grad_out_row_stride,
                                 void* grad_rows, float* grad_w, int64_t N, int64_t T, int64_t D,
                                 int dtype, void* stream) {
+  FMOE_RANGE("fmoe_combine_bwd");
   FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_combine_bwd: bad dtype %d", dtype);
   FMOE_REQUIRE(N >= 0 && T >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_combine_bwd: negative size");
   FMOE_REQUIRE(N < (1ll << 31) && T < (1ll << 31) - 1, FMOE_ERR_UNSUPPORTED,
@@ -605,6 +607,7 @@ extern "C" int fmoe_combine_bwd(const void* plan, const void* grad_out, int64_t 
 extern "C" int fmoe_permute_fwd(const void* x, int64_t x_row_stride, const int32_t* slot_of,
                                 void* permuted, int64_t T, int64_t K, int64_t D, int dtype,
                                 void* stream) {
+  FMOE_RANGE("fmoe_permute_fwd");
   FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_permute_fwd: bad dtype %d", dtype);
   FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_permute_fwd: negative size");
   FMOE_REQUIRE(T * K < (1ll << 31), FMOE_ERR_UNSUPPORTED, "fmoe_permute_fwd: T*K must fit in int32");
@@ -647,6 +650,7 @@ extern "C" int fmoe_permute_fwd(const void* x, int64_t x_row_stride, const int32
 extern "C" int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_of, void* grad_x,
                                 int64_t grad_x_row_stride, int64_t T, int64_t K, int64_t D,
                                 int dtype, void* stream) {
+  FMOE_RANGE("fmoe_permute_bwd");
   FMOE_REQUIRE(valid_dtype(dtype), FMOE_ERR_ARG, "fmoe_permute_bwd: bad dtype %d", dtype);
   FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_permute_bwd: negative size");
   FMOE_REQUIRE(T * K < (1ll << 31), FMOE_ERR_UNSUPPORTED, "fmoe_permute_bwd: T*K must fit in int32");
@@ -669,6 +673,7 @@ extern "C" int fmoe_permute_bwd(const void* grad_permuted, const int32_t* slot_o
 extern "C" int fmoe_combine_routed(const void* rows, const int32_t* slot_of, const void* w_sorted, int w_dtype,
                                    void* out, int64_t out_row_stride, int64_t T, int64_t K, int64_t D, int dtype,
                                    int accumulate, void* stream) {
+  FMOE_RANGE("fmoe_combine_routed");
   FMOE_REQUIRE(valid_dtype(dtype) && valid_dtype(w_dtype), FMOE_ERR_ARG, "fmoe_combine_routed: bad dtype %d / %d",
                dtype, w_dtype);
   FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_combine_routed: negative size");
@@ -690,6 +695,7 @@ extern "C" int fmoe_combine_routed(const void* rows, const int32_t* slot_of, con
 extern "C" int fmoe_combine_routed_bwd(const void* rows, const int32_t* slot_of, const void* w_sorted, int w_dtype,
                                        const void* grad_out, int64_t grad_out_row_stride, void* grad_rows,
                                        float* grad_w, int64_t T, int64_t K, int64_t D, int dtype, void* stream) {
+  FMOE_RANGE("fmoe_combine_routed_bwd");
   FMOE_REQUIRE(valid_dtype(dtype) && valid_dtype(w_dtype), FMOE_ERR_ARG,
                "fmoe_combine_routed_bwd: bad dtype %d / %d", dtype, w_dtype);
   FMOE_REQUIRE(T >= 0 && K >= 0 && D >= 0, FMOE_ERR_ARG, "fmoe_combine_routed_bwd: negative size");
@@ -779,6 +785,7 @@ __global__ void __launch_bounds__(256)
 
 extern "C" int fmoe_gelu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t n,
                              void* stream) {
+  FMOE_RANGE("fmoe_gelu_bwd");
   FMOE_REQUIRE(rows >= 0 && n >= 0, FMOE_ERR_ARG, "fmoe_gelu_bwd: negative size");
   FMOE_REQUIRE(n % 8 == 0, FMOE_ERR_UNSUPPORTED, "fmoe_gelu_bwd: n=%lld must be a multiple of 8", (long long)n);
   if (rows == 0 || n == 0) return FMOE_OK;
@@ -795,11 +802,13 @@ extern "C" int fmoe_gelu_bwd(const void* h, const void* grad_act, void* grad_h, 
 
 extern "C" int fmoe_swiglu_bwd(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
                                void* stream) {
+  FMOE_RANGE("fmoe_swiglu_bwd");
   return fmoe_swiglu_bwd_ragged(h, grad_act, grad_h, rows, ff, nullptr, stream);
 }
 
 extern "C" int fmoe_swiglu_bwd_ragged(const void* h, const void* grad_act, void* grad_h, int64_t rows, int64_t ff,
                                       const int64_t* rows_used, void* stream) {
+  FMOE_RANGE("fmoe_swiglu_bwd_ragged");
   FMOE_REQUIRE(rows >= 0 && ff >= 0, FMOE_ERR_ARG, "fmoe_swiglu_bwd: negative size");
   FMOE_REQUIRE(ff % 8 == 0, FMOE_ERR_UNSUPPORTED, "fmoe_swiglu_bwd: ff=%lld must be a multiple of 8", (long long)ff);
   if (rows == 0 || ff == 0) return FMOE_OK;
