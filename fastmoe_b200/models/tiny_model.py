@@ -447,7 +447,9 @@ class PipelinedMoEBlock(nn.Module):
         n_mb = self.num_micro_batches
         if n_mb is None:
             n_mb = 2 if self.moe.world_size > 1 else 1
-        if n_mb == 1:  # nothing to overlap: the plain block on the caller's stream
+        if n_mb == 1 or getattr(self.moe, "_fused_exchange", None) is not None:
+            # nothing to overlap here: one micro-batch, or the fused exchange, which overlaps the
+            # dispatch of one expert group with the GEMMs of the previous one inside the layer
             x = x + self.attn(self.norm1(x))
             return x + self.moe(self.norm2(x))
         chunks = x.chunk(n_mb, dim=0)
