@@ -898,9 +898,10 @@ def run_gemm(args, rank, world, local_rank):
                      "peak": peak, "peak_kind": kind, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                      "gate_up_ms": gate_up_ms, "gate_up_tflops": 4 * R * D * FF / gate_up_ms / 1e9,
                      "down_ms": down_ms, "down_tflops": 2 * R * D * FF / down_ms / 1e9,
-                     "fwd_bwd_ms": fb_ms, "fwd_bwd_tflops": 4 * flops / fb_ms / 1e9,
-                     "fwd_bwd_note": "3x the forward products plus the gate/up recomputation (4x flops), "
-                                     "SwiGLU derivative as elementwise torch code in between"},
+                     "fwd_bwd_ms": fb_ms, "fwd_bwd_tflops": 3 * flops / fb_ms / 1e9,
+                     "fwd_bwd_note": "forward + data and weight gradients of both products = 3x the forward "
+                                     "FLOPs (the forward keeps its pre-activations, nothing is recomputed), "
+                                     "SwiGLU derivative as one streaming kernel in between"},
         "clocks": clocks.summary(),
     }  # fmt: skip
     print(json.dumps(line), flush=True)

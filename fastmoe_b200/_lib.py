@@ -47,6 +47,7 @@ SIGNATURES = {
     "fmoe_permute_fwd": (c_int, [_P, _L, _P, _P, _L, _L, _L, _I, _P]),
     "fmoe_permute_bwd": (c_int, [_P, _P, _P, _L, _L, _L, _L, _I, _P]),
     "fmoe_grouped_gemm": (c_int, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
+    "fmoe_grouped_gemm_keep_pre": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P, _P]),
     "fmoe_grouped_gemm_dgrad": (c_int, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "fmoe_grouped_gemm_wgrad": (c_int, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _P, _P]),
     "fmoe_swiglu_bwd": (c_int, [_P, _P, _P, _L, _L, _P]),

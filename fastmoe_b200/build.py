@@ -54,7 +54,7 @@ def build(verbose: bool = False, force: bool = True) -> Path:
     nvcc = _nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libfastmoe_b200.so")
-    cmd = [nvcc, *NVCC_FLAGS]
+    cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("FASTMOE_B200_NVCC_FLAGS", "").split()]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     tmp = LIB_PATH.with_suffix(".so.tmp")

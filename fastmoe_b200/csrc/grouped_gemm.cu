@@ -38,7 +38,9 @@ struct GemmArgs {
   const int64_t* c_row_map;  // optional [R]: row of C that receives the result of A's row r (nullptr = r)
   const int64_t* c_row_ptrs;  // optional [R]: ADDRESS of the output row of A's row r (may be peer memory)
   __nv_bfloat16* C;
+  __nv_bfloat16* pre;      // optional [R, N]: the product BEFORE the activation, by A's row (for a backward pass)
   int64_t ldc;             // row stride of C in elements
+  int64_t ld_pre;          // row stride of pre in elements (N)
   int64_t R;               // rows of A
   int E;
   int n_blocks;            // column tiles per expert
@@ -408,6 +410,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // swizzled staging buffer so that every store instruction writes four complete
       // 128-byte row segments: full lines for HBM, full packets for NVLink peers.
       uint4* stage_w = stage + (warp - 2) * (32 * 8);
+      // a training forward keeps the product before the activation: this lane's row of `pre`
+#ifdef FMOE_NO_KEEP_PRE  // build switch for A/B measurements of the epilogue without this path
+      __nv_bfloat16* pre_row = nullptr;
+#else
+      __nv_bfloat16* pre_row = (valid && a.pre != nullptr) ? a.pre + (c.row0 + row) * a.ld_pre : nullptr;
+#endif
+      auto keep = [&](const uint32_t* v, int64_t col) {  // 32 consecutive columns of one row, 64 bytes
+        float t[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) t[i] = __uint_as_float(v[i]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(pre_row + col + 8 * q) = pack16<FMOE_BF16>(t + 8 * q);
+      };
 #pragma unroll 1
       for (int c0 = 0; c0 < out_cols; c0 += 64) {
 #pragma unroll
@@ -418,12 +433,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tmem_ld32(taddr + c0 + 32 * h, g);
             tmem_ld32(taddr + 128 + c0 + 32 * h, u);
             tmem_ld_wait();
+            if (pre_row != nullptr) {  // gate columns first, up columns behind them, as the weights lie
+              const int64_t col = static_cast<int64_t>(c.nb) * 128 + c0 + 32 * h;
+              keep(g, col);
+              keep(u, a.up_row_offset + col);
+            }
 #pragma unroll
             for (int i = 0; i < 32; ++i) f[i] = silu(__uint_as_float(g[i])) * __uint_as_float(u[i]);
           } else {
             uint32_t r[32];
             tmem_ld32(taddr + c0 + 32 * h, r);
             tmem_ld_wait();
+            if (pre_row != nullptr) keep(r, static_cast<int64_t>(c.nb) * kBN + c0 + 32 * h);
             if (a.gelu) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) f[i] = gelu_erf(__uint_as_float(r[i]));
@@ -1058,11 +1079,35 @@ static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t co
 
 using namespace fmoe;
 
+static int grouped_gemm_impl(const void* a, const void* w, void* c, void* pre, const int64_t* offsets,
+                             const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
+                             int64_t E, int64_t R, int64_t N, int64_t K, int activation, int32_t* status,
+                             void* stream);
+
 extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offsets,
                                  const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
                                  int64_t E, int64_t R, int64_t N, int64_t K, int activation, int32_t* status,
                                  void* stream) {
   FMOE_RANGE("fmoe_grouped_gemm");
+  return grouped_gemm_impl(a, w, c, nullptr, offsets, counts, c_row_map, c_row_ptrs, E, R, N, K, activation, status,
+                           stream);
+}
+
+extern "C" int fmoe_grouped_gemm_keep_pre(const void* a, const void* w, void* c, void* pre, const int64_t* offsets,
+                                          const int64_t* counts, const int64_t* c_row_map,
+                                          const int64_t* c_row_ptrs, int64_t E, int64_t R, int64_t N, int64_t K,
+                                          int activation, int32_t* status, void* stream) {
+  FMOE_RANGE("fmoe_grouped_gemm_keep_pre");
+  FMOE_REQUIRE(pre != nullptr && aligned_to(pre, 16), FMOE_ERR_ARG,
+               "fmoe_grouped_gemm_keep_pre: pre must be a 16-byte aligned [R, N] buffer");
+  return grouped_gemm_impl(a, w, c, pre, offsets, counts, c_row_map, c_row_ptrs, E, R, N, K, activation, status,
+                           stream);
+}
+
+static int grouped_gemm_impl(const void* a, const void* w, void* c, void* pre, const int64_t* offsets,
+                             const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
+                             int64_t E, int64_t R, int64_t N, int64_t K, int activation, int32_t* status,
+                             void* stream) {
   FMOE_REQUIRE(activation >= FMOE_ACT_NONE && activation <= FMOE_ACT_GELU, FMOE_ERR_ARG,
                "fmoe_grouped_gemm: activation must be FMOE_ACT_NONE, FMOE_ACT_SWIGLU or FMOE_ACT_GELU");
   const int swiglu = activation == FMOE_ACT_SWIGLU;
@@ -1084,7 +1129,9 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
                "fmoe_grouped_gemm: null pointer argument");
   FMOE_REQUIRE(aligned_to(a, 16) && aligned_to(w, 16) && aligned_to(c, 16), FMOE_ERR_ARG,
                "fmoe_grouped_gemm: a, w and c must be 16-byte aligned");
-  const bool tokens_as_n = g_gemm_tokens_as_n == 1 || (g_gemm_tokens_as_n < 0 && R / E < kTnAutoRows);
+  // (the tokens-as-N kernel does not keep pre-activations: a training forward takes the other one)
+  const bool tokens_as_n =
+      pre == nullptr && (g_gemm_tokens_as_n == 1 || (g_gemm_tokens_as_n < 0 && R / E < kTnAutoRows));
   if (tokens_as_n) {
     CUtensorMap map_t, map_wt;
     int rc_t = make_map(&map_t, a, R, K, "A (64-row boxes)", kTnLoadRows);
@@ -1131,7 +1178,9 @@ extern "C" int fmoe_grouped_gemm(const void* a, const void* w, void* c, const in
   g.c_row_map = c_row_map;
   g.c_row_ptrs = c_row_ptrs;
   g.C = static_cast<__nv_bfloat16*>(c);
+  g.pre = static_cast<__nv_bfloat16*>(pre);
   g.ldc = swiglu ? N / 2 : N;
+  g.ld_pre = N;
   g.R = R;
   g.E = static_cast<int>(E);
   g.n_blocks = static_cast<int>(swiglu ? (N / 2) / 128 : N / kBN);
@@ -1185,6 +1234,8 @@ extern "C" int fmoe_grouped_gemm_dgrad(const void* grad_c, const void* w, void* 
   g.c_row_map = nullptr;
   g.c_row_ptrs = row_ptrs;
   g.C = static_cast<__nv_bfloat16*>(grad_a);
+  g.pre = nullptr;
+  g.ld_pre = 0;
   g.ldc = K;
   g.R = R;
   g.E = static_cast<int>(E);

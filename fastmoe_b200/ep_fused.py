@@ -199,15 +199,19 @@ class FusedExpertParallel:
             self._grad = (g_recv, g_ret, self._peer_addresses(h1, g_recv), self._peer_addresses(h2, g_ret), h1, h2)
         return self._grad[:4]
 
-    def _exchange_and_experts(self, x_flat, topk_idx, ix, lay: _Layout):
+    def _exchange_and_experts(self, x_flat, topk_idx, ix, lay: _Layout, keep_pre=False):
         """Dispatch, both grouped GEMMs and the return trip for all expert groups; ends with the
         barrier after which this rank's return buffer holds every expert output for its tokens.
-        Returns the activations between the two GEMMs ([cap_rows, ff], for a backward)."""
+        Returns the activations between the two GEMMs ([cap_rows, ff]) and, with `keep_pre`, the
+        gate/up products before the activation ([cap_rows, 2*ff]): what a backward needs."""
         moe, K, D, G = self.moe, self.top_k, self.dim, self.expert_groups
         el = moe.num_local_experts
         recv = self._recv.view(self.cap_rows, D)
         w_gate_up, w_down = moe.experts.w_gate_up, moe.experts.w_down
         hidden = torch.empty(self.cap_rows, w_down.shape[2], dtype=torch.bfloat16, device=x_flat.device)
+        pre = None
+        if keep_pre:
+            pre = torch.empty(self.cap_rows, w_gate_up.shape[1], dtype=torch.bfloat16, device=x_flat.device)
 
         def send(lo, hi):
             self._send_rows(x_flat, topk_idx, ix.slot_of, K, ix.offsets, lay.dst_row0, self.recv_bases, self._ret,
@@ -215,7 +219,7 @@ class FusedExpertParallel:
 
         def run_experts(lo, hi):
             off, cnt = lay.offsets_local[lo:hi], lay.counts_local[lo:hi]
-            experts._launch(recv, w_gate_up[lo:hi], off, cnt, True, out=hidden)
+            experts._launch(recv, w_gate_up[lo:hi], off, cnt, True, out=hidden, pre=pre)
             experts._launch(hidden, w_down[lo:hi], off, cnt, False, row_ptrs=lay.row_ptrs)
 
         if G == 1:
@@ -238,9 +242,9 @@ class FusedExpertParallel:
                     run_experts(g * eg, (g + 1) * eg)
                 self._barrier()  # every expert output for my tokens has landed
             main.wait_stream(hi)
-            return hidden
+            return hidden, pre
         self._barrier()  # every expert output for my tokens has landed
-        return hidden
+        return hidden, pre
 
     def experts_over_peers(self, x_flat, topk_idx, ix):
         """Expert outputs for the routed rows of `x_flat`, in this rank's sorted-slot order
@@ -300,17 +304,17 @@ class _FusedExperts(torch.autograd.Function):
         n_rows = x_flat.shape[0] * K
         lay = fx._layout(counts, with_grad_ptrs=True)
         ix = routing.RoutingIndex(None, None, counts, offsets, None, slot_of)
-        hidden = fx._exchange_and_experts(x_flat, topk_idx, ix, lay)
+        hidden, pre = fx._exchange_and_experts(x_flat, topk_idx, ix, lay, keep_pre=True)
         ctx.fx, ctx.k = fx, K
         ctx.generation = fx._generation
         ctx.save_for_backward(w_gate_up, w_down, slot_of, offsets, counts, lay.dst_row0, lay.counts_local,
-                              lay.offsets_local, lay.rows_used, lay.grad_row_ptrs, hidden)  # fmt: skip
+                              lay.offsets_local, lay.rows_used, lay.grad_row_ptrs, hidden, pre)  # fmt: skip
         return fx._ret.view(fx.max_rows, D)[:n_rows]
 
     @staticmethod
     def backward(ctx, grad_rows):
         (w_gate_up, w_down, slot_of, offsets, counts, dst_row0, counts_local, offsets_local, rows_used,
-         back_ptrs, hidden) = ctx.saved_tensors  # fmt: skip
+         back_ptrs, hidden, pre) = ctx.saved_tensors  # fmt: skip
         fx, K = ctx.fx, ctx.k
         if ctx.generation != fx._generation:
             raise RuntimeError(
@@ -338,8 +342,7 @@ class _FusedExperts(torch.autograd.Function):
         ff = w_down.shape[2]
         grad_hidden = experts._dgrad(grad_y, w_down, offsets_local, counts_local, covers_all_rows=True)
         grad_w_down = experts._wgrad(grad_y, hidden, w_down.shape, offsets_local, counts_local)
-        pre = experts._launch(recv, w_gate_up, offsets_local, counts_local, False, covers_all_rows=True)
-        grad_pre = torch.empty_like(pre)
+        grad_pre = torch.empty_like(pre)  # `pre`: the gate/up products the forward's epilogue kept
         ops._call("fmoe_swiglu_bwd_ragged", 1, pre.data_ptr(), grad_hidden.data_ptr(), grad_pre.data_ptr(),
                   pre.shape[0], ff, rows_used.data_ptr(), _stream_ptr(dev))  # fmt: skip
         grad_w_gate_up = experts._wgrad(grad_pre, recv, w_gate_up.shape, offsets_local, counts_local)

@@ -9,8 +9,8 @@ in `MoEFeedForward.compute_experts` of polkadot21/fastmoe (tiny_model.py:282-294
 
 Forward, data gradient and weight gradient all run on the hand-written tcgen05 kernels
 (`csrc/grouped_gemm.cu`) with the per-expert row ranges read from device memory; the
-activation's derivative between them is one streaming kernel over recomputed
-pre-activations. Shapes the kernels do not tile raise ValueError, forward and backward
+activation's derivative between them is one streaming kernel over the pre-activations,
+which a forward that will be differentiated stores from its epilogue beside the result. Shapes the kernels do not tile raise ValueError, forward and backward
 alike: there is no library fallback.
 """
 
@@ -67,10 +67,11 @@ def _after_launch(device, what):
                                + (" (a bounded wait gave up)" if value & _lib.STATUS_WAIT_TIMEOUT else ""))  # fmt: skip
 
 
-def _launch(a, w, offsets, counts, act, row_map=None, covers_all_rows=False, row_ptrs=None, out=None):
+def _launch(a, w, offsets, counts, act, row_map=None, covers_all_rows=False, row_ptrs=None, out=None, pre=None):
     """One grouped GEMM launch. `act` is ACT_NONE / ACT_SWIGLU / ACT_GELU (False / True also
     mean the first two). `out` ([R, cols], bf16, contiguous) receives the result instead of a
-    fresh tensor; with `row_ptrs` every row goes where its table entry points."""
+    fresh tensor; with `row_ptrs` every row goes where its table entry points. `pre` ([R, N],
+    bf16, contiguous) also receives the product before the activation, row r of `a` in row r."""
     a, w = a.contiguous(), w.contiguous()
     act = int(act)
     R, K = a.shape
@@ -86,32 +87,42 @@ def _launch(a, w, offsets, counts, act, row_map=None, covers_all_rows=False, row
         c = torch.empty(R, cols, dtype=torch.bfloat16, device=a.device)
     else:  # rows that belong to no expert are never written: start from zeros so they are defined
         c = torch.zeros(R, cols, dtype=torch.bfloat16, device=a.device)
-    ops._call(
-        "fmoe_grouped_gemm", 1, a.data_ptr(), w.data_ptr(), c.data_ptr() if c is not None else None,
-        offsets.data_ptr(), counts.data_ptr(), row_map.data_ptr() if row_map is not None else None,
-        row_ptrs.data_ptr() if row_ptrs is not None else None, E, R, N, K,
-        act, _status_word(a.device).data_ptr(), _stream_ptr(a.device),
-    )  # fmt: skip
+    tail = (offsets.data_ptr(), counts.data_ptr(), row_map.data_ptr() if row_map is not None else None,
+            row_ptrs.data_ptr() if row_ptrs is not None else None, E, R, N, K,
+            act, _status_word(a.device).data_ptr(), _stream_ptr(a.device))  # fmt: skip
+    c_ptr = c.data_ptr() if c is not None else None
+    if pre is None:
+        ops._call("fmoe_grouped_gemm", 1, a.data_ptr(), w.data_ptr(), c_ptr, *tail)
+    else:
+        if pre.shape != (R, N) or pre.dtype != torch.bfloat16 or not pre.is_contiguous():
+            raise ValueError(f"pre must be a contiguous bfloat16 [{R}, {N}] tensor")
+        ops._call("fmoe_grouped_gemm_keep_pre", 1, a.data_ptr(), w.data_ptr(), c_ptr, pre.data_ptr(), *tail)
     _after_launch(a.device, "fmoe_grouped_gemm")
     return c
 
 
 class _GroupedGemm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, a, w, offsets, counts, act, row_map, covers_all_rows):
-        ctx.save_for_backward(a, w, offsets, counts, row_map)
+    def forward(ctx, a, w, offsets, counts, act, row_map, covers_all_rows, keep_pre):
+        # a forward that will be differentiated keeps the product before the activation (the
+        # epilogue stores it beside the result), so that the backward needs no second product
+        pre = None
+        if keep_pre and act != ACT_NONE:
+            pre = torch.empty(a.shape[0], w.shape[1], dtype=torch.bfloat16, device=a.device)
+        out = _launch(a, w, offsets, counts, act, row_map, covers_all_rows, pre=pre)
+        ctx.save_for_backward(a, w, offsets, counts, row_map, pre)
         ctx.act, ctx.covers_all_rows = act, covers_all_rows
-        return _launch(a, w, offsets, counts, act, row_map, covers_all_rows)
+        return out
 
     @staticmethod
     def backward(ctx, grad_c):
-        a, w, offsets, counts, row_map = ctx.saved_tensors
+        a, w, offsets, counts, row_map, h = ctx.saved_tensors
         if row_map is not None:
             grad_c = grad_c.index_select(0, row_map)  # back to the row order of `a`
         grad_c = grad_c.contiguous()
         if ctx.act != ACT_NONE:
-            # recompute the pre-activations with the plain kernel, then the activation's derivative
-            h = _launch(a, w, offsets, counts, ACT_NONE, covers_all_rows=ctx.covers_all_rows)
+            if h is None:  # the forward ran without keeping them: recompute with the plain kernel
+                h = _launch(a, w, offsets, counts, ACT_NONE, covers_all_rows=ctx.covers_all_rows)
             grad_h = torch.empty_like(h)
             if ctx.act == ACT_SWIGLU:
                 ops._call("fmoe_swiglu_bwd", 1, h.data_ptr(), grad_c.data_ptr(), grad_h.data_ptr(), h.shape[0],
@@ -124,7 +135,7 @@ class _GroupedGemm(torch.autograd.Function):
         need_a, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         grad_a = _dgrad(grad_c, w, offsets, counts, ctx.covers_all_rows) if need_a else None
         grad_w = _wgrad(grad_c, a, w.shape, offsets, counts) if need_w else None
-        return grad_a, grad_w, None, None, None, None, None
+        return grad_a, grad_w, None, None, None, None, None, None
 
 
 def _apply(a, w, offsets, counts, act, row_map, covers_all_rows):
@@ -136,7 +147,7 @@ def _apply(a, w, offsets, counts, act, row_map, covers_all_rows):
         raise ValueError("row_map must be an int64 device tensor with one entry per row of a")
     training = torch.is_grad_enabled() and (a.requires_grad or w.requires_grad)
     check_shapes(w.shape[1], w.shape[2], act, training)
-    return _GroupedGemm.apply(a, w, offsets, counts, act, row_map, covers_all_rows)
+    return _GroupedGemm.apply(a, w, offsets, counts, act, row_map, covers_all_rows, training)
 
 
 def _dgrad(grad_c, w, offsets, counts, covers_all_rows=False, row_ptrs=None):

@@ -106,6 +106,8 @@ class GroupedSwiGLUExperts(nn.Module):
 
 
 class MoEFeedForward(nn.Module):
+    grouped_gelu_min_experts = 16  # local GELU experts from which the FAST bf16 path runs them grouped
+
     def __init__(self, dim, ff_dim, num_experts, top_k, implementation, group=None, expert_type="gelu"):
         super().__init__()
         self.dim, self.num_experts, self.top_k = dim, num_experts, top_k
@@ -260,9 +262,15 @@ class MoEFeedForward(nn.Module):
             return False
         if self.expert_type == "swiglu":
             return recv_data.dtype == torch.bfloat16
-        # GELU experts: bf16 modules and rows, or any under bf16 autocast, and only widths the
-        # kernels tile (forward and, when training, backward); everything else keeps the
-        # per-expert modules, exactly as the reference runs them
+        # GELU experts: bf16 modules and rows, or any under bf16 autocast, only widths the
+        # kernels tile (forward and, when training, backward), and only with many experts, where
+        # the reference's loop is bound by its 2 x E launches (256 experts of width 256: 243 ->
+        # 192 ms per training step). A handful of large experts (8 of 8192 x 8192) run as fast
+        # as per-expert library products and need no stacked copy of the weights (measured 259 ms
+        # per step in the loop against 282 ms grouped), so everything else keeps the modules,
+        # exactly as the reference runs them
+        if len(self.experts) < self.grouped_gelu_min_experts:
+            return False
         fc1 = self.experts[0][0].weight
         in_bf16 = fc1.dtype == torch.bfloat16 and recv_data.dtype == torch.bfloat16
         if not fc1.is_cuda or not (in_bf16 or self._autocast_bf16()):

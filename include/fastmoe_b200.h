@@ -348,6 +348,17 @@ int fmoe_grouped_gemm(const void* a, const void* w, void* c, const int64_t* offs
                       int64_t E, int64_t R, int64_t N, int64_t K, int activation, int32_t* status,
                       void* stream);
 
+/* The same product for a forward pass that will be differentiated: besides C it stores the
+ * product BEFORE the activation into pre ([R, N] bf16, row r of A -> row r of pre, whatever
+ * c_row_map / c_row_ptrs do to C; for FMOE_ACT_SWIGLU the gate columns followed by the up
+ * columns), so that the backward's activation derivative (fmoe_swiglu_bwd, fmoe_gelu_bwd)
+ * needs no second product. What autograd keeps of Linear's output before the activation in
+ * MoEFeedForward.compute_experts (src/fastmoe/models/tiny_model.py:282-294). */
+int fmoe_grouped_gemm_keep_pre(const void* a, const void* w, void* c, void* pre, const int64_t* offsets,
+                               const int64_t* counts, const int64_t* c_row_map, const int64_t* c_row_ptrs,
+                               int64_t E, int64_t R, int64_t N, int64_t K, int activation, int32_t* status,
+                               void* stream);
+
 /*
  * Data gradient of the plain grouped GEMM: grad_a[rows of e, :K] = grad_c[rows of e, :N] x W[e]
  * (W[e] is [N, K], read as it lies in memory: its N rows are the reduction dimension and

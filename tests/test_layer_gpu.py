@@ -219,6 +219,8 @@ def test_gelu_experts_run_grouped_in_bf16_and_match_the_per_expert_modules():
     T, D, FF, E, K = 384, 256, 512, 8, 2
     fast = MoEFeedForward(D, FF, E, K, MoEImplementation.FAST).to(DEV).bfloat16()
     std = MoEFeedForward(D, FF, E, K, MoEImplementation.STANDARD).to(DEV).bfloat16()
+    assert not fast._use_grouped(torch.zeros(4, D, device=DEV).bfloat16())  # 8 experts: below the threshold
+    fast.grouped_gelu_min_experts = 1  # the layer takes the grouped path from this many local experts on
     assert "experts.3.0.weight" in fast.state_dict() and "experts.3.2.weight" in fast.state_dict()
     with torch.no_grad():
         for prm in fast.parameters():
