@@ -67,8 +67,8 @@ class FusedExpertParallel:
     set on the sender and on the receiver, and `check_status()` turns that into an exception
     at a step boundary of the caller's choice.
     expert_groups: groups the local experts are split into for the overlap described in the
-    module docstring (None = 4 with several ranks, or 2 or 1 if 4 does not divide the local
-    experts; 1 in a group of one rank, where nothing crosses NVLink).
+    module docstring (None = 4 with several ranks, fewer if the rank holds fewer experts; 1 in
+    a group of one rank, where nothing crosses NVLink). The first group is half an even share.
     barrier_timeout_ms: bound of every wait for the other ranks inside `fmoe_peer_barrier`.
     """
 
@@ -94,10 +94,11 @@ class FusedExpertParallel:
         self.cap_rows = max(128, (self.cap_rows + 127) // 128 * 128)
         el = moe.num_local_experts
         if expert_groups is None:
-            expert_groups = next(g for g in (4, 2, 1) if el % g == 0) if self.world > 1 else 1
-        if expert_groups < 1 or el % expert_groups:
-            raise ValueError(f"expert_groups={expert_groups} does not divide the {el} local experts")
+            expert_groups = min(4, el) if self.world > 1 else 1
+        if expert_groups < 1 or expert_groups > el:
+            raise ValueError(f"expert_groups={expert_groups} must lie between 1 and the {el} local experts")
         self.expert_groups = int(expert_groups)
+        self.group_bounds = self._group_bounds(el, self.expert_groups)
         self.barrier_timeout_ms = int(barrier_timeout_ms)
         self._recv = symm_mem.empty(self.cap_rows * self.dim, dtype=torch.bfloat16, device=self.device)
         self._ret = symm_mem.empty(self.max_rows * self.dim, dtype=torch.bfloat16, device=self.device)
@@ -120,6 +121,17 @@ class FusedExpertParallel:
         self._grad = None
         torch.cuda.synchronize(self.device)  # the flags are zero before anybody's first barrier
         dist.barrier(self.group)
+
+    @staticmethod
+    def _group_bounds(el, groups):
+        """First local expert of every group, and `el` at the end. The first group is half the
+        size of an even share: its rows cross NVLink before any GEMM can start, so it is the one
+        part of the exchange that nothing hides; the others share the rest evenly."""
+        if groups == 1:
+            return [0, el]
+        first = max(1, el // (2 * groups))
+        rest = el - first
+        return [0] + [first + rest * g // (groups - 1) for g in range(groups)]
 
     def _peer_addresses(self, handle, tensor):
         """Device array with the address of `tensor`'s first byte in every rank's mapping. The
@@ -227,19 +239,20 @@ class FusedExpertParallel:
             self._barrier()  # all rows for my experts have landed
             run_experts(0, el)
         else:
-            main, side, hi, eg = torch.cuda.current_stream(self.device), self._side, self._gemm_stream, el // G
+            main, side, hi = torch.cuda.current_stream(self.device), self._side, self._gemm_stream
+            bounds = self.group_bounds
             side.wait_stream(main)
             hi.wait_stream(main)
             arrived = []
             with torch.cuda.stream(side):
                 for g in range(G):
-                    send(g * eg, (g + 1) * eg)
+                    send(bounds[g], bounds[g + 1])
                     self._barrier(1)  # group g's rows have landed on every rank
                     arrived.append(side.record_event())
             with torch.cuda.stream(hi):
                 for g in range(G):
                     hi.wait_event(arrived[g])
-                    run_experts(g * eg, (g + 1) * eg)
+                    run_experts(bounds[g], bounds[g + 1])
                 self._barrier()  # every expert output for my tokens has landed
             main.wait_stream(hi)
             return hidden, pre

@@ -328,3 +328,30 @@ def test_expert_parallel_layer_sized_products():
             assert err_h <= 1e-2 and err_y <= 1e-2, (E, e, err_h, err_y)
         del x, wgu, wd, hidden, y
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("act", ["swiglu", "gelu"])
+def test_training_forward_keeps_the_products_before_the_activation(act):
+    """fmoe_grouped_gemm_keep_pre: the result is what the plain entry point gives, and `pre`
+    holds the product before the activation (gate columns, then up columns, for SwiGLU), row r of
+    A in row r of `pre` even when the result rows are scattered through a row map; rows that
+    belong to no expert are left alone."""
+    counts, K, N = [200, 0, 5, 300], 256, 512
+    a, w, off, cnt = _case(counts, K, N, act == "swiglu", seed=71)
+    pad = torch.zeros(24, K, device=DEV, dtype=torch.bfloat16)
+    a = torch.cat([a, pad], 0)  # 24 rows behind the last expert
+    R = a.shape[0]
+    code = experts.ACT_SWIGLU if act == "swiglu" else experts.ACT_GELU
+    perm = torch.randperm(R, device=DEV)
+    want = experts._launch(a, w, off, cnt, code, row_map=perm)
+    pre = torch.full((R, N), 3.0, dtype=torch.bfloat16, device=DEV)
+    got = experts._launch(a, w, off, cnt, code, row_map=perm, pre=pre)
+    plain = experts._launch(a, w, off, cnt, experts.ACT_NONE)
+    torch.cuda.synchronize()
+    assert ops.read_status() == 0
+    used = sum(counts)
+    assert torch.equal(got[perm[:used]], want[perm[:used]])
+    assert torch.equal(pre[:used], plain[:used])
+    assert bool((pre[used:] == 3.0).all()), "rows of no expert were written"
+    with pytest.raises(ValueError):
+        experts._launch(a, w, off, cnt, code, pre=pre[:, : N // 2].contiguous())

@@ -109,3 +109,17 @@ def test_swiglu_expert_container_behaves_like_a_module_list():
     h = x @ ex.w_gate_up[1].t()
     want = (torch.nn.functional.silu(h[:, :4]) * h[:, 4:]) @ ex.w_down[1].t()
     assert torch.allclose(ex[1](x), want)
+
+
+def test_expert_groups_cover_the_local_experts_with_a_small_first_group():
+    """Group boundaries of the fused exchange's overlap: contiguous, non-empty, covering every
+    local expert once; the first group (whose transfer nothing hides) is about half an even share."""
+    from fastmoe_b200.ep_fused import FusedExpertParallel
+
+    for el, groups in ((64, 4), (32, 4), (128, 4), (4, 4), (8, 4), (8, 2), (1, 1), (3, 2), (256, 1), (5, 5)):
+        b = FusedExpertParallel._group_bounds(el, groups)
+        assert b[0] == 0 and b[-1] == el and len(b) == groups + 1
+        assert all(b[i] < b[i + 1] for i in range(groups))
+        if groups > 1 and el >= 4 * groups:
+            assert b[1] - b[0] <= (el // groups + 1) // 2 + 1 <= b[2] - b[1]
+    assert FusedExpertParallel._group_bounds(64, 4) == [0, 8, 26, 45, 64]
