@@ -621,6 +621,8 @@ def ep_layer_bench(rank, world, local_rank, steps, warmup, micro_batches=None, m
                 from fastmoe_b200.ep_fused import FusedExpertParallel
 
                 fused = FusedExpertParallel(moe, max_tokens=T, expert_groups=expert_groups)
+                if os.environ.get("FASTMOE_B200_EP_STAGGER") is not None:  # A/B switch for measurements
+                    fused.stagger_copies = os.environ["FASTMOE_B200_EP_STAGGER"] != "0"
                 ep_mode = "fused peer stores"
             except Exception as exc:  # symmetric memory unavailable: every rank falls back alike
                 ep_mode = f"nccl all_to_all (fused path unavailable: {type(exc).__name__})"

@@ -99,6 +99,7 @@ class FusedExpertParallel:
             raise ValueError(f"expert_groups={expert_groups} must lie between 1 and the {el} local experts")
         self.expert_groups = int(expert_groups)
         self.group_bounds = self._group_bounds(el, self.expert_groups)
+        self.stagger_copies = True  # see _exchange_and_experts
         self.barrier_timeout_ms = int(barrier_timeout_ms)
         self._recv = symm_mem.empty(self.cap_rows * self.dim, dtype=torch.bfloat16, device=self.device)
         self._ret = symm_mem.empty(self.max_rows * self.dim, dtype=torch.bfloat16, device=self.device)
@@ -243,16 +244,28 @@ class FusedExpertParallel:
             bounds = self.group_bounds
             side.wait_stream(main)
             hi.wait_stream(main)
-            arrived = []
-            with torch.cuda.stream(side):
-                for g in range(G):
+
+            def send_group(g):
+                with torch.cuda.stream(side):
                     send(bounds[g], bounds[g + 1])
                     self._barrier(1)  # group g's rows have landed on every rank
-                    arrived.append(side.record_event())
-            with torch.cuda.stream(hi):
-                for g in range(G):
-                    hi.wait_event(arrived[g])
+                    return side.record_event()
+
+            arrived = send_group(0)
+            for g in range(G):
+                with torch.cuda.stream(hi):
+                    hi.wait_event(arrived)
+                    gemm_starts = hi.record_event()
+                if g + 1 < G:
+                    # the next group's copy starts with this group's gate/up GEMM (which does not
+                    # touch NVLink) rather than as soon as the previous copy is done: it then
+                    # competes less with the down-projection's stores to the other GPUs
+                    if self.stagger_copies:
+                        side.wait_event(gemm_starts)
+                    arrived = send_group(g + 1)
+                with torch.cuda.stream(hi):
                     run_experts(bounds[g], bounds[g + 1])
+            with torch.cuda.stream(hi):
                 self._barrier()  # every expert output for my tokens has landed
             main.wait_stream(hi)
             return hidden, pre
