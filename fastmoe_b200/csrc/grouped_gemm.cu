@@ -218,7 +218,7 @@ __device__ __forceinline__ TileCoord locate_tile(int tile, const int* mb_prefix,
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                        const GemmArgs a) {  // map_w: box 64 x 128 rows (forward) or 64 x 64 rows (w_transposed)
+                        const GemmArgs a) {  // map_w: box 64 x 256 rows (plain), 64 x 128 (SwiGLU) or 64 x 64 (w_transposed)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       } else {
         const int r0 = expert * a.w_rows_per_expert + nb * (a.swiglu ? 128 : kBN);
         tma_prefetch_2d(&map_w, kb * kBK, r0);
-        tma_prefetch_2d(&map_w, kb * kBK, r0 + a.up_row_offset);
+        if (a.swiglu) tma_prefetch_2d(&map_w, kb * kBK, r0 + a.up_row_offset);
       }
     };
     const int ahead = a.prefetch < a.k_blocks ? a.prefetch : a.k_blocks;
@@ -336,9 +336,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int piece = 0; piece < 4; ++piece)
             tma_load_2d(smem_b + stage * kBBytes + piece * (kBBytes / 4), &map_w, c.nb * kBN + piece * 64, red_row,
                         &full[stage]);
-        } else {
+        } else if (a.swiglu) {
           tma_load_2d(smem_b + stage * kBBytes, &map_w, kb * kBK, w_row0, &full[stage]);
           tma_load_2d(smem_b + stage * kBBytes + kBBytes / 2, &map_w, kb * kBK, w_row1, &full[stage]);
+        } else {  // 256 consecutive weight rows: one box (the TMA unit's cost is per box as well as per byte)
+          tma_load_2d(smem_b + stage * kBBytes, &map_w, kb * kBK, w_row0, &full[stage]);
         }
         ++fills;
         if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -1169,7 +1171,7 @@ static int grouped_gemm_impl(const void* a, const void* w, void* c, void* pre, c
   CUtensorMap map_a, map_w;
   int rc = make_map(&map_a, a, R, K, "A");
   if (rc != 0) return rc;
-  rc = make_map(&map_w, w, E * N, K, "W");
+  rc = make_map(&map_w, w, E * N, K, "W", swiglu ? 128 : 256);
   if (rc != 0) return rc;
 
   GemmArgs g;
