@@ -19,6 +19,9 @@ Rank 0 prints ONE JSON line. Keys beyond the usual ones:
   cpu_baseline  the reference's own CPU path (the unmodified package, when
             oracle/install_ref.py has installed it; else its C port in oracle/),
             timed in this run on a stated sample of the same workload
+  graph_replay  the form the reference's microbenchmark times (zero `out`, replay a
+            CUDA graph of the call with prebuilt metadata), with and without the
+            zero-fill; one GPU only, outside the headline timing
   also      the other single-GPU configurations, a few steps each, outside the
             headline timing: the skewed (Zipf) combine and the dispatch + combine
             chain under autograd, each with its own roofline entry
@@ -398,6 +401,56 @@ def combine_record(name, rank, world, device, steps, warmup, keep=False):
     return (rec, wl, out) if keep else (rec, None, None)
 
 
+def graph_replay_record(wl, shape, steps):
+    """The combine as the reference's microbenchmark times it (run_on_cloud.py:64-91): metadata
+    built once, the call with `out=` and `metadata=` captured in a CUDA graph, every step zeroes
+    `out` and replays. The call ADDS into `out`, so against the headline form (a fresh result)
+    each step also writes the zeros and reads them back: T*D*s more bytes each way
+    (`extra_bytes_per_step`), which `value` does not count."""
+    import torch
+
+    from fastmoe_b200.kernels import ops
+
+    out = torch.zeros(shape, device=wl.indices.device, dtype=wl.experts[0].dtype)
+    metadata = ops.prepare_grouped_metadata(wl.experts, out.device)
+
+    def launch():
+        ops.grouped_weighted_scatter_add(wl.experts, wl.indices, wl.weights, shape, out=out, metadata=metadata)
+
+    launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    out.zero_()
+    with torch.cuda.graph(graph):
+        launch()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for with_zero in (True, False):  # the second pass leaves the zero-fill out and keeps adding
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            if with_zero:
+                out.zero_()
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        if with_zero:
+            ms_zero = start.elapsed_time(end) / steps
+            fresh = ops.grouped_weighted_scatter_add(wl.experts, wl.indices, wl.weights, shape)
+            assert torch.equal(out, fresh), "graph replay into a zeroed output differs from the plain call"
+            del fresh
+        else:
+            ms_plain = start.elapsed_time(end) / steps
+    nbytes = wl.algorithmic_bytes()
+    return {
+        "form": "out.zero_() + replay of a CUDA graph of grouped_weighted_scatter_add(out=, metadata=)",
+        "steps": steps, "ms_per_step": ms_zero, "value": nbytes / (ms_zero / 1e3) / 1e9, "unit": UNIT,
+        "ms_per_step_without_zero_fill": ms_plain, "value_without_zero_fill": nbytes / (ms_plain / 1e3) / 1e9,
+        "extra_bytes_per_step": 2 * out.numel() * out.element_size(),
+    }  # fmt: skip
+
+
 def roofline_of(rec, name):
     peak, peak_kind = measured_peak()
     achieved = rec["bytes"] / (rec["kernel_ms"] / 1e3) / 1e9 if rec["kernel_ms"] else None
@@ -443,6 +496,10 @@ def run_ours(args, rank, world, local_rank):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # ---- the reference's own timing form: zero `out`, replay a CUDA graph of the call with
+    # prebuilt metadata (run_on_cloud.py:64-91); at N=1, outside the headline timing ------
+    graph_rec = graph_replay_record(wl, (T, D), max(3, min(args.steps, 20))) if world == 1 else None
 
     # ---- end to end through the C ABI with host buffers ----------------------------
     host = host_copy(wl)
@@ -556,6 +613,7 @@ def run_ours(args, rank, world, local_rank):
             "pinned_buffers": (f"allocated after binding the rank to its GPU's {local_cores} local cores"
                                if local_cores else "allocated with the process's default affinity"),
         },
+        "graph_replay": graph_rec,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "call": "fmoe_combine_host (C ABI, pinned host buffers)"},
         "gpu_launches": rec["launches"],
