@@ -499,7 +499,9 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- the reference's own timing form: zero `out`, replay a CUDA graph of the call with
     # prebuilt metadata (run_on_cloud.py:64-91); at N=1, outside the headline timing ------
-    graph_rec = graph_replay_record(wl, (T, D), max(3, min(args.steps, 20))) if world == 1 else None
+    graph_rec = None
+    if world == 1 and not args.no_also:
+        graph_rec = graph_replay_record(wl, (T, D), max(3, min(args.steps, 20)))
 
     # ---- end to end through the C ABI with host buffers ----------------------------
     host = host_copy(wl)
@@ -1100,7 +1102,7 @@ def main():
                     help="expert-parallel layer, fused exchange: groups the local experts are split into for the "
                          "overlap of dispatch and GEMMs (default: 4 with several ranks)")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel layer part of the default run")
-    ap.add_argument("--no-also", action="store_true", help="skip the skewed-combine and dispatch+combine sub-records")
+    ap.add_argument("--no-also", action="store_true", help="skip the graph-replay, skewed-combine and dispatch+combine sub-records")
     ap.add_argument("--cpu-port", action="store_true",
                     help="CPU baseline: time the C port even where the reference package is installed")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
