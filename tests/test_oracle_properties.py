@@ -118,3 +118,55 @@ def test_bad_inputs_are_refused():
         oracle.combine(experts, np.array([0, -1, 1]), w, 4)
     with pytest.raises(ValueError):
         oracle.combine(experts, idx[:2], w[:2], 4)
+
+
+@pytest.mark.parametrize("T,E,K,world", [(1, 1, 1, 1), (37, 8, 2, 1), (64, 16, 4, 4), (200, 256, 8, 8)])
+def test_routing_oracle_invariants(T, E, K, world):
+    """Top-k picks the K largest logits in descending order (equal values: lower expert id
+    first), the gate weights are a softmax over the selected values, and the index is the stable
+    expert-major sort of the T*K routed slots with its exact inverse."""
+    from oracle import routing
+
+    rng = np.random.default_rng(11)
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    if E > 2:
+        logits[0, 1] = logits[0, 2] = logits[0].max() + 1.0  # a tie at the top of token 0
+    idx, w = routing.topk_softmax(logits, K)
+    assert idx.shape == (T, K) and idx.dtype == np.int64 and w.dtype == np.float32
+    picked = np.take_along_axis(logits, idx, -1)
+    assert (np.diff(picked, axis=-1) <= 0).all()
+    assert (np.sort(logits, -1)[:, ::-1][:, :K] == picked).all()
+    assert all(len(set(row)) == K for row in idx.tolist())
+    if E > 2 and K >= 2:
+        assert idx[0, 0] == 1 and idx[0, 1] == 2
+    assert np.allclose(w.sum(-1), 1.0, atol=1e-6) and (w > 0).all()
+    want = np.exp(picked - picked.max(-1, keepdims=True))
+    assert np.allclose(w, want / want.sum(-1, keepdims=True), rtol=1e-6, atol=1e-7)
+
+    ix = routing.build_index(idx, w, E, world)
+    N = T * K
+    flat_e, flat_w = idx.reshape(-1), w.reshape(-1)
+    order = np.argsort(flat_e, kind="stable")
+    assert np.array_equal(ix["reverse_map"], order // K)
+    assert np.array_equal(ix["sorted_w"], flat_w[order])
+    assert np.array_equal(ix["counts"], np.bincount(flat_e, minlength=E))
+    assert np.array_equal(ix["offsets"], np.cumsum(ix["counts"]) - ix["counts"])
+    assert int(ix["counts"].sum()) == N
+    assert np.array_equal(ix["expert_counts_by_rank"], ix["counts"].reshape(world, E // world))
+    assert np.array_equal(ix["rank_counts"], ix["counts"].reshape(world, -1).sum(1))
+    assert ix["slot_of"].dtype == np.int32 and np.array_equal(order[ix["slot_of"]], np.arange(N))
+    # every expert's segment of the sorted order holds its own slots in ascending routed position
+    sorted_e = flat_e[order]
+    assert (np.diff(sorted_e) >= 0).all()
+    same = np.diff(sorted_e) == 0
+    assert (np.diff(order)[same] > 0).all()
+
+
+def test_metadata_oracle_handles_empty_and_ragged_experts():
+    from oracle import routing
+
+    sizes, offsets, max_rows, n = routing.prepare_metadata([3, 0, 5, 0])
+    assert sizes.dtype == np.int32 and offsets.dtype == np.int64
+    assert sizes.tolist() == [3, 0, 5, 0] and offsets.tolist() == [0, 3, 3, 8] and (max_rows, n) == (5, 4)
+    sizes, offsets, max_rows, n = routing.prepare_metadata([])
+    assert len(sizes) == 0 and len(offsets) == 0 and (max_rows, n) == (0, 0)
