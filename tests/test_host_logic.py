@@ -123,3 +123,36 @@ def test_expert_groups_cover_the_local_experts_with_a_small_first_group():
         if groups > 1 and el >= 4 * groups:
             assert b[1] - b[0] <= (el // groups + 1) // 2 + 1 <= b[2] - b[1]
     assert FusedExpertParallel._group_bounds(64, 4) == [0, 8, 26, 45, 64]
+
+
+@pytest.mark.parametrize("world,el,seed", [(1, 1, 0), (1, 5, 1), (2, 3, 2), (4, 2, 3), (8, 4, 4), (3, 7, 5)])
+def test_fused_layout_against_a_row_by_row_simulation_of_the_exchange(world, el, seed):
+    """The placement arithmetic of the fused exchange, held against the exchange done one row at a
+    time in plain Python: every rank's rows (expert-major, as the index builder leaves them) are
+    appended to the owner's receive list in (local expert, source rank) order."""
+    from fastmoe_b200 import exchange
+
+    E, row_bytes = world * el, 16
+    gen = torch.Generator().manual_seed(seed)
+    C = torch.randint(0, 6, (world, E), generator=gen)
+    C[torch.rand(world, E, generator=gen) < 0.3] = 0  # experts that a rank sends nothing to
+    starts = torch.cumsum(C, 1) - C  # first sorted slot of expert e on rank s
+    received = {d: [] for d in range(world)}  # (source rank, source slot, local expert) per receive row
+    first_row = {}  # (source rank, global expert) -> row on the owner where that source's rows begin
+    for d in range(world):
+        for le in range(el):
+            g = d * el + le
+            for s in range(world):
+                first_row[(s, g)] = len(received[d])
+                received[d] += [(s, int(starts[s, g]) + i, le) for i in range(int(C[s, g]))]
+    for rank in range(world):
+        total = len(received[rank])
+        for cap in (total + 3, max(total - 2, 0)):
+            dst_row0, counts, offsets, src_rank, origin_byte, used = exchange.fused_layout(C, rank, cap, row_bytes)
+            assert dst_row0.tolist() == [first_row[(rank, g)] for g in range(E)]
+            kept = received[rank][:cap]
+            assert int(used) == len(kept)
+            assert counts.tolist() == [sum(1 for r in kept if r[2] == le) for le in range(el)]
+            assert offsets.tolist() == [min(sum(1 for r in received[rank] if r[2] < le), cap) for le in range(el)]
+            assert src_rank[: len(kept)].tolist() == [r[0] for r in kept]
+            assert origin_byte[: len(kept)].tolist() == [r[1] * row_bytes for r in kept]
